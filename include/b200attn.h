@@ -36,7 +36,7 @@
 extern "C" {
 #endif
 
-#define B2_ABI_VERSION 3
+#define B2_ABI_VERSION 4
 
 #if defined(__GNUC__)
 #define B2_API __attribute__((visibility("default")))
@@ -466,7 +466,7 @@ B2_API int b2_comm_allgather_cols(void* comm, const void* local, int64_t local_s
 
 /* ---------------------------------------------------------------------------------------------
  * Building blocks of decoders beyond the Llama layer (hyper_norm.cu, delta_rule.cu, chunk_attention.cu, moe.cu,
- * post_norm.cu, latent_attention.cu).
+ * post_norm.cu, latent_attention.cu, group_norm.cu).
  * Every op exists for two activation types: B2_ACT_BF16 (weights, activations and caches in bf16) and B2_ACT_F32
  * (everything in fp32).  The residual streams, all statistics, softmax, router logits and recurrent state are fp32 in
  * both.  Small parameter vectors (norm weights, convolution taps, gates' constants, router bias, stream mixing) are
@@ -493,9 +493,35 @@ B2_API int b2_delta_scan(const float* qkv, const float* beta, const float* decay
                          float* state, float* o, void* stream);
 B2_API int b2_delta_out(const float* o, const void* proj, int64_t proj_stride, int off_g, int act_dtype, int T, int H,
                         int dv, const float* norm_w, float eps, void* out, int64_t out_stride, void* stream);
+/* The stages of b2_delta_* with their constants as parameters (delta_rule.cu): optional convolution / SiLU / unit vectors,
+ * a decay per head or per key channel, the delta correction or the plain outer product as the write, a SiLU or sigmoid
+ * output gate given as a row of its own. */
+#define B2_DECAY_HEAD_SOFTPLUS        0   /* decay [T, H]      = exp(-exp(A_log[h]) softplus(proj[off_a + h] + bias[h])) */
+#define B2_DECAY_CHANNEL_SOFTPLUS     1   /* decay [T, H, dk]  = exp(-exp(A_log[h]) softplus(a[h, i] + bias[h, i])) */
+#define B2_DECAY_CHANNEL_SIGMOID_POW  2   /* decay [T, H, dk]  = sigmoid(a[h, i] + bias[h, i]) ^ (1 / tau) */
+#define B2_GATE_SILU    0
+#define B2_GATE_SIGMOID 1
+B2_API int b2_recur_prep(const void* proj, int64_t proj_stride, int act_dtype, int T, int H, int G, int dk, int dv,
+                         int taps, const float* conv_w /* NULL with taps = 1: no convolution */, int conv_silu, int unit,
+                         float unit_eps, float q_scale, int off_beta /* < 0: none */, int decay_mode, int off_a,
+                         const float* a /* fp32 [T, H*dk], channel modes */, int64_t a_stride, const float* A_log,
+                         const float* decay_bias /* [H] or [H*dk]; may be NULL in the channel modes */, float tau,
+                         const int32_t* cu_q, const int32_t* ctx_start, const int32_t* state_slot, int n_seq,
+                         void* conv_state, float* qkv, float* beta, float* decay, void* stream);
+B2_API int b2_channel_scan(const float* qkv, const float* beta /* NULL without delta */, const float* decay, int total_rows,
+                           int H, int G, int dk, int dv, int decay_per_channel, int delta, const int32_t* cu_q,
+                           const int32_t* ctx_start, const int32_t* state_slot, int n_seq, float* state, float* o,
+                           void* stream);
+B2_API int b2_gated_head_norm(const float* o, const void* gate, int64_t gate_stride, int gate_kind, int act_dtype, int T,
+                              int H, int dv, const float* norm_w, float eps, float out_scale, void* out,
+                              int64_t out_stride, void* stream);
 B2_API int b2_qknorm_cache(const void* qkv, int64_t qkv_stride, int act_dtype, int T, int H, int G, int dk, int dv,
                            const float* q_w, const float* k_w, float eps, const int64_t* slots, int bs, void* q_out,
                            void* k_cache, void* v_cache, void* stream);
+B2_API int b2_qk_prep_cache(const void* qkv, int64_t qkv_stride, int act_dtype, int T, int H, int G, int dk, int dv,
+                            int norm, const float* q_w, const float* k_w, float eps, const int32_t* positions,
+                            float temp_coef, int temp_every, const int64_t* slots, int bs, void* q_out, void* k_cache,
+                            void* v_cache, void* stream);
 B2_API int b2_chunk_attention(void* out, const void* q, const void* k_cache, const void* v_cache, int act_dtype,
                               const int32_t* block_tables, int max_nb, const int32_t* cu_q, const int32_t* ctx_start,
                               int n_seq, int T, int H, int G, int dk, int dv, int bs, float scale, int chunk, float sink,
@@ -504,12 +530,21 @@ B2_API int b2_moe_tile_rows(void);
 B2_API int b2_moe_capacity(int n, int E);
 #define B2_ROUTE_TOPK_SOFTMAX 0   /* top-k of logits + bias, weights = softmax over the chosen logits */
 #define B2_ROUTE_SOFTMAX_ALL  1   /* s = softmax over all experts, top-k of s + bias, weights = the chosen s as they are */
+#define B2_ROUTE_SIGMOID_GROUPED 2 /* s = sigmoid, choice by s + bias inside the keep_groups best of n_groups groups (group score =
+                                   * its two largest s + bias), weights = chosen s / (their sum + 1e-20) * weight_scale */
 #define B2_GLU_SILU    0          /* silu(g) * u */
 #define B2_GLU_CLAMPED 1          /* g' = min(g, limit), u' = clamp(u, -limit, limit): g' * sigmoid(alpha g') * (u' + 1) */
+#define B2_GLU_GELU_TANH 2        /* gelu_tanh(g) * u (b2_glu_and_mul only) */
+#define B2_FF_RELU_SQ  3          /* no gate: max(u, 0)^2 (b2_moe_experts only; w_gate is not read) */
 B2_API int b2_moe_route(const void* h, int64_t h_stride, const void* w_router, const float* bias, int act_dtype, int T,
                         int D, int E, int top, int scoring, int32_t* ids, float* weights, void* stream);
 B2_API int b2_moe_select(const float* logits, int64_t stride, const float* bias, int T, int E, int top, int scoring,
                          int32_t* ids, float* weights, void* stream);
+B2_API int b2_moe_route_ex(const void* h, int64_t h_stride, const void* w_router, const float* bias, int act_dtype, int T,
+                           int D, int E, int top, int scoring, int n_groups, int keep_groups, float weight_scale,
+                           int32_t* ids, float* weights, void* stream);
+B2_API int b2_moe_select_ex(const float* logits, int64_t stride, const float* bias, int T, int E, int top, int scoring,
+                            int n_groups, int keep_groups, float weight_scale, int32_t* ids, float* weights, void* stream);
 B2_API int b2_moe_align(const int32_t* ids, int n, int E, int cap, int32_t* sorted, int32_t* tile_expert, int32_t* place,
                         int32_t* group_ends /* [E] or NULL */, void* stream);
 B2_API int b2_moe_gather(const void* h, int64_t h_stride, int act_dtype, const int32_t* sorted, int cap, int top, int D,
@@ -529,7 +564,21 @@ B2_API int b2_relu_sq(void* out, int64_t out_stride, const void* in, int64_t in_
                       void* stream);
 B2_API int b2_glu_and_mul(void* out, int64_t out_stride, const void* gate_up, int64_t in_stride, int act_dtype, int T, int I,
                           int glu, float alpha, float limit, void* stream);
+B2_API int b2_gate_mul(void* out, int64_t out_stride, const void* x, int64_t x_stride, const void* gate, int64_t gate_stride,
+                       int act_dtype, int T, int I, int kind, float scale, void* stream);
 B2_API int b2_softcap(void* z, int64_t stride, int act_dtype, int T, int V, float cap, void* stream);
+/* group_norm.cu: sinusoidal-position embedding, RMS norm in groups with a per-channel scale on the sublayer output and a
+ * token shift (blend with the previous token's normalised row, kept per sequence in fp32 state slots) on the read-out */
+B2_API int b2_embed_sinusoid_norm(float* x, const void* embed, int act_dtype, const int64_t* tokens,
+                                  const int32_t* positions, int T, int D, const double* freq /* [ceil(D/2)] */,
+                                  const float* norm_w /* or NULL */, int groups, float eps, void* stream);
+B2_API int b2_group_norm_step(const float* x_in, float* x_out, int T, int D, const void* y, int64_t y_stride,
+                              const float* y_scale, const float* y_bias, const float* norm_w, int groups, float eps,
+                              const float* shift_mu /* or NULL */, const float* shift_state /* [slots, D] */,
+                              const int32_t* cu_q, const int32_t* ctx_start, const int32_t* state_slot, int n_seq, void* h,
+                              int64_t h_stride, int act_dtype, void* stream);
+B2_API int b2_shift_state(const float* x, int D, const float* norm_w, int groups, float eps, const int32_t* cu_q,
+                          const int32_t* ctx_start, const int32_t* state_slot, int n_seq, float* shift_state, void* stream);
 /* latent_attention.cu: attention over one shared low-rank latent + one shared rotated key part per token */
 B2_API int b2_latent_prep(const void* proj, int64_t proj_stride, int act_dtype, int T, int H, int dn, int dr, int rot_dims,
                           int R, int q_off, int dkv_off /* < 0: the layer reads another layer's pool */, const float* norm_w,

@@ -406,9 +406,10 @@ class LlamaModel:
 
 
 def _register_families() -> None:
-    from . import gatolix, kofadra
+    from . import gatolix, kofadra, tonilix
     ARCHITECTURES[kofadra.ARCHITECTURE] = kofadra.config_from_dir
     ARCHITECTURES[gatolix.ARCHITECTURE] = gatolix.config_from_dir
+    ARCHITECTURES[tonilix.ARCHITECTURE] = tonilix.config_from_dir
 
 
 _register_families()

@@ -642,8 +642,9 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor] = None, see
 # ======================================================================================================================
 from dataclasses import dataclass  # noqa: E402
 
-from ._lib import (ACT_BF16, ACT_F32, GLU_CLAMPED, GLU_SILU, NORM_LAYER, NORM_RMS,  # noqa: E402,F401
-                   ROUTE_SOFTMAX_ALL, ROUTE_TOPK_SOFTMAX)
+from ._lib import (ACT_BF16, ACT_F32, DECAY_CHANNEL_SIGMOID_POW, DECAY_CHANNEL_SOFTPLUS,  # noqa: E402,F401
+                   DECAY_HEAD_SOFTPLUS, FF_RELU_SQ, GATE_SIGMOID, GATE_SILU, GLU_CLAMPED, GLU_GELU_TANH, GLU_SILU, NORM_LAYER,
+                   NORM_RMS, ROUTE_SIGMOID_GROUPED, ROUTE_SOFTMAX_ALL, ROUTE_TOPK_SOFTMAX)
 
 
 def _act(t: torch.Tensor, name: str) -> int:
@@ -845,10 +846,12 @@ def chunk_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
 
 
 def moe_route(h: torch.Tensor, w_router: torch.Tensor, bias: Optional[torch.Tensor], top: int,
-              scoring: int = ROUTE_TOPK_SOFTMAX):
+              scoring: int = ROUTE_TOPK_SOFTMAX, n_groups: int = 1, keep_groups: int = 1, weight_scale: float = 1.0):
     """ids int32 [T, top], weights fp32 [T, top] from the fp32 logits z = h W_r^T.  ROUTE_TOPK_SOFTMAX: the top z + bias,
     weights = softmax over the chosen; ROUTE_SOFTMAX_ALL: s = softmax(z) over all experts, the top s + bias are chosen,
-    weights = their s, not renormalised."""
+    weights = their s, not renormalised; ROUTE_SIGMOID_GROUPED: s = sigmoid(z), the top s + bias inside the `keep_groups`
+    of `n_groups` groups of neighbouring experts with the largest sum of their two best s + bias, weights = the chosen s
+    over their sum, times weight_scale."""
     lib = _lib.load()
     dev = _need_cuda(h=h, w_router=w_router, bias=bias)
     T, D, hs = _mat(h, "h")
@@ -858,13 +861,14 @@ def moe_route(h: torch.Tensor, w_router: torch.Tensor, bias: Optional[torch.Tens
     _f32(bias, "bias", (E,))
     ids = torch.empty(T, top, dtype=torch.int32, device=dev)
     wts = torch.empty(T, top, dtype=torch.float32, device=dev)
-    if T >= MOE_ROUTE_GEMM_MIN_ROWS and E * 4 * 4 <= 48 * 1024:
+    if T >= MOE_ROUTE_GEMM_MIN_ROWS and E * 4 * 4 * 3 <= 48 * 1024:
         # the logits are a GEMM (bf16 operands, fp32 accumulation and fp32 result; fp32 as it is)
         z = torch.mm(h, w_router.t(), out_dtype=torch.float32) if h.dtype == torch.bfloat16 else torch.mm(h, w_router.t())
-        _lib.check(lib.b2_moe_select(_ptr(z), E, _ptr(bias), T, E, top, int(scoring), _ptr(ids), _ptr(wts), _stream(dev)))
+        _lib.check(lib.b2_moe_select_ex(_ptr(z), E, _ptr(bias), T, E, top, int(scoring), int(n_groups), int(keep_groups),
+                                        float(weight_scale), _ptr(ids), _ptr(wts), _stream(dev)))
         return ids, wts
-    _lib.check(lib.b2_moe_route(_ptr(h), hs, _ptr(w_router), _ptr(bias), _act(h, "h"), T, D, E, top, int(scoring), _ptr(ids),
-                                _ptr(wts), _stream(dev)))
+    _lib.check(lib.b2_moe_route_ex(_ptr(h), hs, _ptr(w_router), _ptr(bias), _act(h, "h"), T, D, E, top, int(scoring),
+                                   int(n_groups), int(keep_groups), float(weight_scale), _ptr(ids), _ptr(wts), _stream(dev)))
     return ids, wts
 
 
@@ -878,11 +882,12 @@ MOE_ROUTE_GEMM_MIN_ROWS = 16
 MOE_GROUPED_GEMM_MIN_PAIRS = 2048
 
 
-def moe_experts(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor,
+def moe_experts(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_gate: Optional[torch.Tensor], w_up: torch.Tensor,
                 w_down: torch.Tensor, w_gate_up: Optional[torch.Tensor] = None, glu: int = GLU_SILU,
                 glu_alpha: float = 1.0, glu_limit: float = 0.0) -> torch.Tensor:
     """y[t] = sum_j wts[t, j] * W_down[e] glu(W_gate[e] h[t], W_up[e] h[t]), e = ids[t, j]; glu = silu(g) * u (GLU_SILU) or
-    the bounded unit min(g, limit) * sigmoid(alpha min(g, limit)) * (clamp(u, +-limit) + 1) (GLU_CLAMPED).
+    the bounded unit min(g, limit) * sigmoid(alpha min(g, limit)) * (clamp(u, +-limit) + 1) (GLU_CLAMPED); FF_RELU_SQ:
+    experts without a gate, y[t] = sum_j wts[t, j] * W_down[e] max(W_up[e] h[t], 0)^2 (w_gate None).
     w_gate, w_up [E, F, D]; w_down [E, D, F]; w_gate_up [E, 2F, D] (optional): the two stacked per expert -- w_gate and
     w_up may be views of it.  Sorting by expert (b2_moe_align), both products and the weighted sum (in fp32, choice order)
     run on the device without a host read: b2_moe_experts, or for large bf16 batches b2_moe_gather -> grouped GEMM ->
@@ -890,12 +895,15 @@ def moe_experts(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_gate: t
     lib = _lib.load()
     dev = _need_cuda(h=h, ids=ids, wts=wts, w_gate=w_gate, w_up=w_up, w_down=w_down)
     T, D, hs = _mat(h, "h")
-    E, F, _ = w_gate.shape
+    E, F, _ = w_up.shape
     top = ids.shape[1]
+    gated = glu != FF_RELU_SQ
+    if gated == (w_gate is None):
+        raise ValueError("gated experts need w_gate, experts without a gate take none")
     for name, w, shape in (("w_gate", w_gate, (E, F, D)), ("w_up", w_up, (E, F, D)), ("w_down", w_down, (E, D, F))):
-        if w.dtype != h.dtype or tuple(w.shape) != shape or w.stride(2) != 1 or w.stride(1) != shape[2]:
+        if w is not None and (w.dtype != h.dtype or tuple(w.shape) != shape or w.stride(2) != 1 or w.stride(1) != shape[2]):
             raise ValueError(f"{name} must be {shape} of h's dtype with contiguous rows")
-    if w_gate.stride(0) != w_up.stride(0) or not w_down.is_contiguous():
+    if (gated and w_gate.stride(0) != w_up.stride(0)) or not w_down.is_contiguous():
         raise ValueError("w_gate / w_up must share their expert stride, w_down must be contiguous")
     if ids.dtype != torch.int32 or not ids.is_contiguous() or tuple(ids.shape) != (T, top):
         raise ValueError("ids must be contiguous int32 [T, top]")
@@ -903,6 +911,8 @@ def moe_experts(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_gate: t
     n = T * top
     cap = lib.b2_moe_capacity(n, E)
     tiles = cap // lib.b2_moe_tile_rows()
+    if not gated:
+        w_gate_up = w_up if w_up.is_contiguous() else None
     grouped = (w_gate_up is not None and h.dtype == torch.bfloat16 and n >= MOE_GROUPED_GEMM_MIN_PAIRS and D % 8 == 0
                and F % 8 == 0 and hasattr(torch, "_grouped_mm"))
     meta = torch.empty(cap + tiles + n + E, dtype=torch.int32, device=dev)
@@ -911,21 +921,247 @@ def moe_experts(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_gate: t
                                 _stream(dev)))
     y = torch.empty(T, D, dtype=h.dtype, device=dev)
     if grouped:
-        if tuple(w_gate_up.shape) != (E, 2 * F, D) or not w_gate_up.is_contiguous() or w_gate_up.dtype != h.dtype:
+        if tuple(w_gate_up.shape) != (E, (2 if gated else 1) * F, D) or not w_gate_up.is_contiguous() or w_gate_up.dtype != h.dtype:
             raise ValueError("w_gate_up must be contiguous [E, 2F, D] of h's dtype")
         a = torch.empty(cap, D, dtype=h.dtype, device=dev)
         _lib.check(lib.b2_moe_gather(_ptr(h), hs, _act(h, "h"), _ptr(srt), cap, top, D, _ptr(a), _stream(dev)))
         gu = torch._grouped_mm(a, w_gate_up.transpose(1, 2), offs=ends)              # [cap, 2F]; rows past the last group unset
-        act = silu_and_mul(gu) if glu == GLU_SILU else glu_and_mul(gu, glu, glu_alpha, glu_limit)
+        if not gated:
+            act = relu_sq(gu)
+        else:
+            act = silu_and_mul(gu) if glu == GLU_SILU else glu_and_mul(gu, glu, glu_alpha, glu_limit)
         rows = torch._grouped_mm(act, w_down.transpose(1, 2), offs=ends)             # [cap, D]
         _lib.check(lib.b2_moe_combine(_ptr(rows), 0, _ptr(place), _ptr(wts), T, top, D, _ptr(y), D, _act(h, "h"), _stream(dev)))
         return y
     act = torch.empty(cap, F, dtype=h.dtype, device=dev)
     rows = torch.empty(cap, D, dtype=torch.float32, device=dev)
-    _lib.check(lib.b2_moe_experts(_ptr(h), hs, _ptr(w_gate), _ptr(w_up), _ptr(w_down), w_gate.stride(0), _act(h, "h"), T, D, F,
+    _lib.check(lib.b2_moe_experts(_ptr(h), hs, _ptr(w_gate), _ptr(w_up), _ptr(w_down), w_up.stride(0), _act(h, "h"), T, D, F,
                                   top, cap, _ptr(srt), _ptr(tile_e), _ptr(place), _ptr(wts), _ptr(act), _ptr(rows), _ptr(y), D,
                                   int(glu), float(glu_alpha), float(glu_limit), _stream(dev)))
     return y
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# csrc/group_norm.cu, and the parameterised stages of csrc/delta_rule.cu / chunk_attention.cu
+# ----------------------------------------------------------------------------------------------------------------------
+def sinusoid_frequencies(D: int, base: float = 10000.0, device=None) -> torch.Tensor:
+    """float64 [ceil(D / 2)]: base^(-2i / D), the frequencies embed_sinusoid_norm multiplies a position with."""
+    i = torch.arange((D + 1) // 2, dtype=torch.float64)
+    return (float(base) ** (-2.0 * i / D)).to(device)
+
+
+def embed_sinusoid_norm(embed: torch.Tensor, tokens: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor,
+                        norm_w: Optional[torch.Tensor], groups: int, eps: float) -> torch.Tensor:
+    """fp32 [T, D]: gnorm(embed[token] + pe(position); norm_w), pe(p)[2i] = sin(p freq[i]), pe(p)[2i+1] = cos(p freq[i]);
+    gnorm divides each of `groups` equal consecutive parts by its own root mean square.  b2_embed_sinusoid_norm."""
+    lib = _lib.load()
+    dev = _need_cuda(embed=embed, tokens=tokens, positions=positions, freq=freq, norm_w=norm_w)
+    T, D = tokens.shape[0], embed.shape[1]
+    if tokens.dtype != torch.int64 or not tokens.is_contiguous() or not embed.is_contiguous():
+        raise ValueError("tokens must be contiguous int64, embed contiguous")
+    if positions.dtype != torch.int32 or positions.shape != (T,) or not positions.is_contiguous():
+        raise ValueError("positions must be contiguous int32 [T]")
+    if freq.dtype != torch.float64 or freq.shape != ((D + 1) // 2,) or not freq.is_contiguous():
+        raise ValueError("freq must be contiguous float64 [ceil(D / 2)]")
+    _f32(norm_w, "norm_w", (D,))
+    x = torch.empty(T, D, dtype=torch.float32, device=dev)
+    _lib.check(lib.b2_embed_sinusoid_norm(_ptr(x), _ptr(embed), _act(embed, "embed"), _ptr(tokens), _ptr(positions), T, D,
+                                          _ptr(freq), _ptr(norm_w), int(groups), float(eps), _stream(dev)))
+    return x
+
+
+def group_norm_step(x: torch.Tensor, y: Optional[torch.Tensor] = None, y_scale: Optional[torch.Tensor] = None,
+                    y_bias: Optional[torch.Tensor] = None, norm_w: Optional[torch.Tensor] = None, groups: int = 1,
+                    eps: float = 1e-6, h_dtype: Optional[torch.dtype] = None, shift_mu: Optional[torch.Tensor] = None,
+                    shift_state: Optional[torch.Tensor] = None, batch: Optional["SeqBatch"] = None,
+                    x_out: Optional[torch.Tensor] = None):
+    """One pass over the fp32 residual x [T, D]: x' = x + y_scale * (y + y_bias) (written to x_out, default x itself), and
+    with norm_w the read-out h = gnorm(x'; norm_w) as h_dtype.  With shift_mu [D] the read-out becomes
+    h[t] + (h[t-1] - h[t]) * shift_mu, the row before a portion's first row coming from shift_state [slots, D] (zeros at
+    position 0), and shift_state is advanced to the sequences' last rows afterwards; with y this needs x_out != x.
+    Returns h (or None).  b2_group_norm_step + b2_shift_state."""
+    lib = _lib.load()
+    dev = _need_cuda(x=x, y=y, y_scale=y_scale, y_bias=y_bias, norm_w=norm_w, shift_mu=shift_mu, shift_state=shift_state,
+                     x_out=x_out)
+    if x.dtype != torch.float32 or x.dim() != 2 or not x.is_contiguous():
+        raise ValueError("x must be contiguous fp32 [T, D]")
+    T, D = x.shape
+    if x_out is None:
+        x_out = x
+    elif x_out.dtype != torch.float32 or x_out.shape != x.shape or not x_out.is_contiguous():
+        raise ValueError("x_out must be contiguous fp32 [T, D]")
+    ys = 0
+    if y is not None:
+        Ty, Dy, ys = _mat(y, "y")
+        if (Ty, Dy) != (T, D):
+            raise ValueError("y must be [T, D]")
+    for n, v in (("y_scale", y_scale), ("y_bias", y_bias), ("norm_w", norm_w), ("shift_mu", shift_mu)):
+        _f32(v, n, (D,))
+    if D % groups:
+        raise ValueError(f"width {D} is not a multiple of {groups} groups")
+    h = None
+    if norm_w is not None:
+        h_dtype = h_dtype or (y.dtype if y is not None else torch.bfloat16)
+        h = torch.empty(T, D, dtype=h_dtype, device=dev)
+        if y is not None and h.dtype != y.dtype:
+            raise ValueError("h_dtype must equal y's dtype")
+    cu = ctx = slots = None
+    n_seq = 0
+    if shift_mu is not None:
+        if h is None or batch is None or batch.state_slots is None or shift_state is None:
+            raise ValueError("a token shift needs norm_w, the batch with its state slots and shift_state")
+        if shift_state.dtype != torch.float32 or not shift_state.is_contiguous() or shift_state.dim() != 2 \
+                or shift_state.shape[1] != D:
+            raise ValueError("shift_state must be contiguous fp32 [slots, D]")
+        if y is not None and x_out.data_ptr() == x.data_ptr():
+            raise ValueError("with y and a token shift the residual is written to another buffer (x_out)")
+        cu, ctx, slots, n_seq = batch.cu_q, batch.ctx_start, batch.state_slots, batch.n_seq
+    act = _act(h if h is not None else y, "h / y") if (h is not None or y is not None) else ACT_BF16
+    _lib.check(lib.b2_group_norm_step(_ptr(x), _ptr(x_out), T, D, _ptr(y), ys, _ptr(y_scale), _ptr(y_bias), _ptr(norm_w),
+                                      int(groups), float(eps), _ptr(shift_mu), _ptr(shift_state), _ptr(cu), _ptr(ctx),
+                                      _ptr(slots), n_seq, _ptr(h), D, act, _stream(dev)))
+    if shift_mu is not None:
+        _lib.check(lib.b2_shift_state(_ptr(x_out), D, _ptr(norm_w), int(groups), float(eps), _ptr(cu), _ptr(ctx), _ptr(slots),
+                                      n_seq, _ptr(shift_state), _stream(dev)))
+    return h
+
+
+def recur_prep(proj: torch.Tensor, H: int, G: int, dk: int, dv: int, batch: SeqBatch, *, taps: int = 1,
+               conv_w: Optional[torch.Tensor] = None, conv_state: Optional[torch.Tensor] = None, conv_silu: bool = False,
+               unit: bool = False, unit_eps: float = 1e-6, q_scale: float = 1.0, off_beta: int = -1,
+               decay_mode: int = DECAY_CHANNEL_SOFTPLUS, off_a: int = -1, a: Optional[torch.Tensor] = None,
+               A_log: Optional[torch.Tensor] = None, decay_bias: Optional[torch.Tensor] = None, tau: float = 1.0):
+    """Inputs of a linear recurrence over a matrix state from projection rows proj [T, >= 2*G*dk + H*dv] whose first columns
+    are q | k | v: optional short causal convolution (taps, conv_w [C, taps], tail in conv_state [slots, taps-1, C]) with
+    optional SiLU, optional unit vectors for the q and k heads (x / sqrt(sum x^2 + unit_eps)), q times q_scale,
+    beta = sigmoid(proj[:, off_beta + h]) when off_beta >= 0, and the decay: DECAY_HEAD_SOFTPLUS [T, H] from proj[:, off_a + h],
+    A_log [H], decay_bias [H]; DECAY_CHANNEL_SOFTPLUS [T, H, dk] = exp(-exp(A_log[h]) softplus(a + decay_bias));
+    DECAY_CHANNEL_SIGMOID_POW [T, H, dk] = sigmoid(a + decay_bias)^(1 / tau), a fp32 [T, H*dk].  Everything after the
+    projection in fp32.  Returns fp32 qkv [T, C], beta [T, H] or None, decay.  b2_recur_prep."""
+    lib = _lib.load()
+    dev = _need_cuda(proj=proj, conv_w=conv_w, conv_state=conv_state, a=a, A_log=A_log, decay_bias=decay_bias)
+    T, P, ps = _mat(proj, "proj")
+    C = 2 * G * dk + H * dv
+    if P < C or (off_beta >= 0 and off_beta + H > P):
+        raise ValueError("proj is narrower than its column map")
+    if conv_w is not None:
+        _f32(conv_w, "conv_w", (C, taps))
+    if taps > 1 and (conv_w is None or conv_state is None or conv_state.dtype != proj.dtype or not conv_state.is_contiguous()
+                     or tuple(conv_state.shape[1:]) != (taps - 1, C)):
+        raise ValueError(f"a convolution needs conv_w and a contiguous conv_state [slots, {taps - 1}, {C}] of proj's dtype")
+    per_channel = decay_mode != DECAY_HEAD_SOFTPLUS
+    a_stride = 0
+    if per_channel:
+        if a is None or a.dtype != torch.float32 or a.dim() != 2 or a.shape != (T, H * dk) or a.stride(1) != 1:
+            raise ValueError("a must be fp32 [T, H*dk]")
+        a_stride = a.stride(0) if T > 1 else H * dk
+        _f32(decay_bias, "decay_bias", (H * dk,))
+    else:
+        if off_a < 0 or off_a + H > P:
+            raise ValueError("off_a outside proj")
+        _f32(decay_bias, "decay_bias", (H,))
+    _f32(A_log, "A_log", (H,))
+    if batch.state_slots is None:
+        raise ValueError("the batch carries no state slots")
+    qkv = torch.empty(T, C, dtype=torch.float32, device=dev)
+    beta = torch.empty(T, H, dtype=torch.float32, device=dev) if off_beta >= 0 else None
+    decay = torch.empty(T, H * (dk if per_channel else 1), dtype=torch.float32, device=dev)
+    _lib.check(lib.b2_recur_prep(_ptr(proj), ps, _act(proj, "proj"), T, H, G, dk, dv, int(taps), _ptr(conv_w), int(conv_silu),
+                                 int(unit), float(unit_eps), float(q_scale), int(off_beta), int(decay_mode), int(off_a), _ptr(a),
+                                 a_stride, _ptr(A_log), _ptr(decay_bias), float(tau), _ptr(batch.cu_q), _ptr(batch.ctx_start),
+                                 _ptr(batch.state_slots), batch.n_seq, _ptr(conv_state), _ptr(qkv), _ptr(beta), _ptr(decay),
+                                 _stream(dev)))
+    return qkv, beta, decay
+
+
+def channel_scan(qkv: torch.Tensor, beta: Optional[torch.Tensor], decay: torch.Tensor, H: int, G: int, dk: int, dv: int,
+                 batch: SeqBatch, state: torch.Tensor, delta: bool = True) -> torch.Tensor:
+    """Per (sequence, head), token after token, over the state S [dk, dv] kept in `state` [slots, H, dk, dv] (fp32):
+    S <- decay * S (decay [T, H]: one factor per head; [T, H*dk]: one per key channel = row of S); then with delta
+    u = beta (v - S^T k), S <- S + k u^T, without S <- S + k v^T; o = S^T q.  Returns o fp32 [T, H, dv].  b2_channel_scan."""
+    lib = _lib.load()
+    dev = _need_cuda(qkv=qkv, beta=beta, decay=decay, state=state)
+    T = qkv.shape[0]
+    _f32(qkv, "qkv", (T, 2 * G * dk + H * dv))
+    if delta:
+        _f32(beta, "beta", (T, H))
+    if decay.dtype != torch.float32 or not decay.is_contiguous() or tuple(decay.shape) not in ((T, H), (T, H * dk)):
+        raise ValueError("decay must be contiguous fp32 [T, H] or [T, H*dk]")
+    per_channel = tuple(decay.shape) == (T, H * dk) and dk > 1
+    if state.dtype != torch.float32 or not state.is_contiguous() or tuple(state.shape[1:]) != (H, dk, dv):
+        raise ValueError(f"state must be contiguous fp32 [slots, {H}, {dk}, {dv}]")
+    o = torch.empty(T, H, dv, dtype=torch.float32, device=dev)
+    _lib.check(lib.b2_channel_scan(_ptr(qkv), _ptr(beta) if delta else None, _ptr(decay), T, H, G, dk, dv, int(per_channel),
+                                   int(delta), _ptr(batch.cu_q), _ptr(batch.ctx_start), _ptr(batch.state_slots), batch.n_seq,
+                                   _ptr(state), _ptr(o), _stream(dev)))
+    return o
+
+
+def gated_head_norm(o: torch.Tensor, gate: torch.Tensor, norm_w: torch.Tensor, eps: float, gate_kind: int = GATE_SILU,
+                    out_scale: float = 1.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """o fp32 [T, H, dv] -> o / rms(o over dv) * norm_w * act(gate) * out_scale as [T, H*dv] of gate's dtype; gate [T, H*dv]
+    (a view with a row stride is fine), act = SiLU or sigmoid.  b2_gated_head_norm."""
+    lib = _lib.load()
+    dev = _need_cuda(o=o, gate=gate, norm_w=norm_w, out=out)
+    T, H, dv = o.shape
+    _f32(o, "o"), _f32(norm_w, "norm_w", (dv,))
+    Tg, W, gs = _mat(gate, "gate")
+    if (Tg, W) != (T, H * dv):
+        raise ValueError("gate must be [T, H*dv]")
+    if out is None:
+        out = torch.empty(T, H * dv, dtype=gate.dtype, device=dev)
+    To, Wo, os_ = _mat(out, "out")
+    if (To, Wo) != (T, H * dv) or out.dtype != gate.dtype:
+        raise ValueError("out must be [T, H*dv] of gate's dtype")
+    _lib.check(lib.b2_gated_head_norm(_ptr(o), _ptr(gate), gs, int(gate_kind), _act(gate, "gate"), T, H, dv, _ptr(norm_w),
+                                      float(eps), float(out_scale), _ptr(out), os_, _stream(dev)))
+    return out
+
+
+def qk_prep_cache(qkv: torch.Tensor, H: int, G: int, dk: int, dv: int, slots: torch.Tensor, k_cache: torch.Tensor,
+                  v_cache: torch.Tensor, positions: Optional[torch.Tensor] = None, temp_coef: float = 0.0,
+                  temp_every: int = 1) -> torch.Tensor:
+    """Rows qkv [T, H*dk + G*dk + G*dv] (biases already added): k and v go to the paged pools at slots[t] (< 0 skips), the
+    query of the token at position p is multiplied by 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1).
+    Returns q [T, H, dk].  b2_qk_prep_cache without a norm."""
+    lib = _lib.load()
+    dev = _need_cuda(qkv=qkv, slots=slots, k_cache=k_cache, v_cache=v_cache, positions=positions)
+    T, P, ps = _mat(qkv, "qkv")
+    if P != H * dk + G * dk + G * dv:
+        raise ValueError("qkv width differs from H*dk + G*dk + G*dv")
+    nb, bs = k_cache.shape[0], k_cache.shape[2]
+    if tuple(k_cache.shape) != (nb, G, bs, dk) or tuple(v_cache.shape) != (nb, G, bs, dv) or not k_cache.is_contiguous() \
+            or not v_cache.is_contiguous() or k_cache.dtype != qkv.dtype or v_cache.dtype != qkv.dtype:
+        raise ValueError("k_cache / v_cache must be contiguous [nb, G, bs, dk] / [nb, G, bs, dv] of qkv's dtype")
+    if slots.dtype != torch.int64 or slots.shape != (T,) or not slots.is_contiguous():
+        raise ValueError("slots must be contiguous int64 [T]")
+    if temp_coef != 0.0 and (positions is None or positions.dtype != torch.int32 or positions.shape != (T,)
+                             or not positions.is_contiguous() or temp_every < 1):
+        raise ValueError("a query temperature needs contiguous int32 positions [T] and a period of at least 1")
+    q = torch.empty(T, H, dk, dtype=qkv.dtype, device=dev)
+    _lib.check(lib.b2_qk_prep_cache(_ptr(qkv), ps, _act(qkv, "qkv"), T, H, G, dk, dv, 0, None, None, 0.0, _ptr(positions),
+                                    float(temp_coef), int(temp_every), _ptr(slots), bs, _ptr(q), _ptr(k_cache), _ptr(v_cache),
+                                    _stream(dev)))
+    return q
+
+
+def gate_mul(x: torch.Tensor, gate: torch.Tensor, kind: int = GATE_SIGMOID, scale: float = 1.0,
+             out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = x * act(gate) * scale over rows [T, I] (views with row strides are fine).  b2_gate_mul."""
+    lib = _lib.load()
+    dev = _need_cuda(x=x, gate=gate, out=out)
+    T, I, xs = _mat(x, "x")
+    Tg, Ig, gs = _mat(gate, "gate")
+    if (Tg, Ig) != (T, I) or gate.dtype != x.dtype:
+        raise ValueError("gate must be [T, I] of x's dtype")
+    if out is None:
+        out = torch.empty(T, I, dtype=x.dtype, device=dev)
+    To, Io, os_ = _mat(out, "out")
+    if (To, Io) != (T, I) or out.dtype != x.dtype:
+        raise ValueError("out must be [T, I] of x's dtype")
+    _lib.check(lib.b2_gate_mul(_ptr(out), os_, _ptr(x), xs, _ptr(gate), gs, _act(x, "x"), T, I, int(kind), float(scale),
+                               _stream(dev)))
+    return out
 
 
 # ----------------------------------------------------------------------------------------------------------------------

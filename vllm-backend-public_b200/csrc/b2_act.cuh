@@ -45,6 +45,14 @@ __device__ __forceinline__ float glu_clamped_f(float g, float u, float alpha, fl
     u = fminf(fmaxf(u, -limit), limit);
     return g * sigmoid_f(alpha * g) * (u + 1.f);
 }
+// tanh form of GELU: z/2 (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+    return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+__device__ __forceinline__ float relu_sq_f(float z) {
+    z = fmaxf(z, 0.f);
+    return z * z;
+}
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
 // four consecutive elements of an activation row (8 or 16 bytes, aligned)

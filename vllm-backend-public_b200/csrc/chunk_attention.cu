@@ -10,6 +10,9 @@
 //
 //   b2_qknorm_cache      per token: q heads normalised into q_out; k heads normalised and written to the K pool, v copied
 //                        to the V pool, through the token's slot (slot < 0 skips the write).
+//   b2_qk_prep_cache     the same pass with the norm optional and a query temperature: the query of the token at position p
+//                        is multiplied by 1 + coef * ln(floor((p + 1) / every) + 1) (fp32), so queries sharpen as the
+//                        context grows in steps of `every` positions (coef = 0: none).
 //   b2_chunk_attention   per (token, head) one warp: scores of 32 keys at a time (a lane per key), online softmax in fp32
 //                        seeded with the sink, P.V with a lane per value column.  With the mask a query touches at most
 //                        `chunk` keys wherever it stands, so prompt chunks and decode rows run the same kernel; a decode
@@ -26,8 +29,11 @@ template <typename T>
 __global__ void qknorm_cache_kernel(const T* __restrict__ qkv, int64_t qkv_stride, int H, int G, int dk, int dv,
                                     const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
                                     const int64_t* __restrict__ slots, int bs, T* __restrict__ q_out,
-                                    T* __restrict__ k_cache, T* __restrict__ v_cache) {
+                                    T* __restrict__ k_cache, T* __restrict__ v_cache, bool norm,
+                                    const int32_t* __restrict__ positions, float temp_coef, int temp_every) {
     const int row = blockIdx.x;
+    float q_factor = 1.f;
+    if (positions && temp_coef != 0.f) q_factor = 1.f + temp_coef * logf((float)((positions[row] + 1) / temp_every + 1));
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
     const T* src = qkv + (size_t)row * qkv_stride;
     const int64_t slot = slots[row];
@@ -36,12 +42,15 @@ __global__ void qknorm_cache_kernel(const T* __restrict__ qkv, int64_t qkv_strid
     for (int hd = wid; hd < H + 2 * G; hd += nw) {
         if (hd < H + G) {                            // q or k head: x / sqrt(mean(x^2) + eps) * w
             const T* v = src + (size_t)hd * dk;
-            float ss = 0.f;
-            for (int i = lane; i < dk; i += 32) {
-                const float x = b2::ld(v + i);
-                ss = fmaf(x, x, ss);
+            float inv = hd < H ? q_factor : 1.f;
+            if (norm) {
+                float ss = 0.f;
+                for (int i = lane; i < dk; i += 32) {
+                    const float x = b2::ld(v + i);
+                    ss = fmaf(x, x, ss);
+                }
+                inv = rsqrtf(b2::warp_sum(ss) / (float)dk + eps) * (hd < H ? q_factor : 1.f);
             }
-            const float inv = rsqrtf(b2::warp_sum(ss) / (float)dk + eps);
             T* dst;
             const float* w;
             if (hd < H) {
@@ -506,7 +515,25 @@ extern "C" int b2_qknorm_cache(const void* qkv, int64_t qkv_stride, int act_dtyp
     const int warps = H + 2 * G < 8 ? H + 2 * G : 8;
     B2_DISPATCH_ACT(act_dtype, A, (qknorm_cache_kernel<A><<<T, warps * 32, 0, st>>>(
         static_cast<const A*>(qkv), qkv_stride, H, G, dk, dv, q_w, k_w, eps, slots, bs, static_cast<A*>(q_out),
-        static_cast<A*>(k_cache), static_cast<A*>(v_cache))));
+        static_cast<A*>(k_cache), static_cast<A*>(v_cache), true, nullptr, 0.f, 1)));
+    B2_CUDA_OK(cudaGetLastError());
+    return B2_OK;
+}
+
+extern "C" int b2_qk_prep_cache(const void* qkv, int64_t qkv_stride, int act_dtype, int T, int H, int G, int dk, int dv,
+                                int norm, const float* q_w, const float* k_w, float eps, const int32_t* positions,
+                                float temp_coef, int temp_every, const int64_t* slots, int bs, void* q_out, void* k_cache,
+                                void* v_cache, void* stream) {
+    B2_REQUIRE(T >= 0 && H > 0 && G > 0 && H % G == 0 && dk > 0 && dv > 0 && bs > 0, B2_EINVAL, "qk_prep_cache: bad sizes");
+    B2_REQUIRE(temp_coef == 0.f || (positions && temp_every >= 1), B2_EINVAL,
+               "qk_prep_cache: a query temperature needs positions and a period of at least 1");
+    if (T == 0) return B2_OK;
+    B2_REQUIRE(qkv && slots && q_out && k_cache && v_cache, B2_EINVAL, "qk_prep_cache: null pointer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int warps = H + 2 * G < 8 ? H + 2 * G : 8;
+    B2_DISPATCH_ACT(act_dtype, A, (qknorm_cache_kernel<A><<<T, warps * 32, 0, st>>>(
+        static_cast<const A*>(qkv), qkv_stride, H, G, dk, dv, q_w, k_w, eps, slots, bs, static_cast<A*>(q_out),
+        static_cast<A*>(k_cache), static_cast<A*>(v_cache), norm != 0, positions, temp_coef, temp_every > 0 ? temp_every : 1)));
     B2_CUDA_OK(cudaGetLastError());
     return B2_OK;
 }

@@ -1,0 +1,229 @@
+// group_norm.cu -- the residual path of a pre-norm decoder whose norm works in groups, whose sublayer outputs pass a
+// learned per-channel scale before the residual sum, and whose sequence mixers read a blend of the current and the
+// previous token's normalised row ("token shift"); plus an embedding that adds sinusoidal positions.
+//
+//   b2_embed_sinusoid_norm   x[t] = gnorm(embed[token[t]] + pe(position[t]); w): the fp32 residual.  pe(p)[2i] = sin(p f_i),
+//                            pe(p)[2i+1] = cos(p f_i) with the frequencies f_i given as a double table; the angle p f_i is
+//                            formed and reduced to [-pi, pi] in double, so it is exact to fp32 at any position.
+//                            norm_w NULL: no norm.
+//   b2_group_norm_step       one pass over residual rows (fp32):
+//                            (1) x_out[t] = x_in[t] + y_scale * (y[t] + y_bias)       (y NULL: x_out = x_in; y_scale NULL: ones)
+//                            (2) when h is given: hn = gnorm(x_out[t]; w), and without a shift h[t] = hn; with shift_mu
+//                                h[t] = hn + (prev - hn) * shift_mu, prev = the same normalised row of the token before:
+//                                computed from row t-1 of the batch when that row belongs to the same sequence, read from
+//                                the sequence's state slot for the first row of a portion with context, zeros at position 0.
+//                            x_out may be x_in unless y and shift_mu are both given (a row's CTA reads its neighbour's
+//                            inputs, which must not have been overwritten).
+//   b2_shift_state           state[slot of sequence i] = gnorm(x[last row of sequence i]; w): what the next portion or
+//                            decode step of that sequence reads as `prev`.  Runs after b2_group_norm_step on the stream.
+//   gnorm(v; w): v is cut into `groups` equal consecutive parts, each divided by sqrt(mean(part^2) + eps), times w.
+// The residual and all statistics are fp32 whatever the activation type.  Reductions run in a fixed order: a row's result
+// does not depend on the batch around it, and the in-kernel `prev` equals what b2_shift_state stores bit for bit.
+#include "b2_act.cuh"
+
+namespace {
+
+constexpr int kNormThreads = 256;
+constexpr int kNormWarps = kNormThreads / 32;
+
+// 1 / sqrt(mean(part^2) + eps) of every group of `row` (shared memory, D = groups * Dg floats) into ginv [groups].
+// `part_sm` holds groups * kNormWarps floats.  Warps split a group when there are fewer groups than warps.  Ends with a
+// barrier.
+__device__ __forceinline__ void group_inverse_rms(const float* row, int groups, int Dg, float eps, float* part_sm, float* ginv) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int wpg = groups >= kNormWarps ? 1 : kNormWarps / groups;          // warps per group
+    if (wpg == 1) {
+        for (int g = wid; g < groups; g += kNormWarps) {
+            const float* v = row + (size_t)g * Dg;
+            float ss = 0.f;
+            for (int i = lane; i < Dg; i += 32) ss = fmaf(v[i], v[i], ss);
+            ss = b2::warp_sum(ss);
+            if (lane == 0) ginv[g] = rsqrtf(ss / (float)Dg + eps);
+        }
+        __syncthreads();
+        return;
+    }
+    if (wid < groups * wpg) {
+        const int g = wid / wpg, part = wid % wpg;
+        const float* v = row + (size_t)g * Dg;
+        float ss = 0.f;
+        for (int i = part * 32 + lane; i < Dg; i += wpg * 32) ss = fmaf(v[i], v[i], ss);
+        ss = b2::warp_sum(ss);
+        if (lane == 0) part_sm[g * kNormWarps + part] = ss;
+    }
+    __syncthreads();
+    if (threadIdx.x < groups) {
+        float ss = 0.f;
+        for (int p = 0; p < wpg; ++p) ss += part_sm[threadIdx.x * kNormWarps + p];
+        ginv[threadIdx.x] = rsqrtf(ss / (float)Dg + eps);
+    }
+    __syncthreads();
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kNormThreads)
+embed_sinusoid_norm_kernel(float* __restrict__ x, const T* __restrict__ embed, const int64_t* __restrict__ tokens,
+                           const int32_t* __restrict__ positions, int D, const double* __restrict__ freq,
+                           const float* __restrict__ norm_w, int groups, float eps) {
+    extern __shared__ __align__(16) float gn_sm[];   // row [D] | parts [groups * warps] | ginv [groups]
+    float* row = gn_sm;
+    float* part_sm = gn_sm + D;
+    float* ginv = part_sm + groups * kNormWarps;
+    const int t = blockIdx.x;
+    const T* e = embed + (size_t)tokens[t] * D;
+    const double p = (double)positions[t];
+    for (int j = threadIdx.x; 2 * j < D; j += blockDim.x) {
+        double a = p * freq[j];
+        a -= 6.283185307179586476925 * rint(a * 0.15915494309189533577);     // into [-pi, pi]
+        float s, c;
+        sincosf((float)a, &s, &c);
+        row[2 * j] = b2::ld(e + 2 * j) + s;
+        if (2 * j + 1 < D) row[2 * j + 1] = b2::ld(e + 2 * j + 1) + c;
+    }
+    __syncthreads();
+    float* xt = x + (size_t)t * D;
+    if (!norm_w) {
+        for (int i = threadIdx.x; i < D; i += blockDim.x) xt[i] = row[i];
+        return;
+    }
+    const int Dg = D / groups;
+    group_inverse_rms(row, groups, Dg, eps, part_sm, ginv);
+    for (int i = threadIdx.x; i < D; i += blockDim.x) xt[i] = row[i] * ginv[i / Dg] * norm_w[i];
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kNormThreads)
+group_norm_step_kernel(const float* __restrict__ x_in, float* __restrict__ x_out, int D, const T* __restrict__ y, int64_t y_stride,
+                       const float* __restrict__ y_scale, const float* __restrict__ y_bias, const float* __restrict__ norm_w,
+                       int groups, float eps, const float* __restrict__ shift_mu, const float* __restrict__ shift_state,
+                       const int32_t* __restrict__ cu_q, const int32_t* __restrict__ ctx_start,
+                       const int32_t* __restrict__ state_slot, int n_seq, T* __restrict__ h, int64_t h_stride) {
+    extern __shared__ __align__(16) float gn_sm[];   // row [D] | prev row [D] (shift) | parts | ginv | pinv
+    const int t = blockIdx.x;
+    float* row = gn_sm;
+    float* prow = gn_sm + D;
+    float* part_sm = gn_sm + (shift_mu ? 2 : 1) * (size_t)D;
+    float* ginv = part_sm + groups * kNormWarps;
+    float* pinv = ginv + groups;
+    int li = 0, ctx = -1, slot = -1;
+    if (shift_mu) {
+        const int seq = b2::seq_of_row(cu_q, n_seq, t);
+        li = t - cu_q[seq];
+        ctx = ctx_start[seq];
+        slot = state_slot[seq];
+    }
+    const bool have_prev = shift_mu && li > 0 && ctx >= 0;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        float v = x_in[(size_t)t * D + i];
+        const float sc = y_scale ? y_scale[i] : 1.f, bi = y_bias ? y_bias[i] : 0.f;
+        if (y) v = fmaf(sc, b2::ld(y + (size_t)t * y_stride + i) + bi, v);
+        row[i] = v;
+        if (x_out && (y || x_out != x_in)) x_out[(size_t)t * D + i] = v;
+        if (have_prev) {
+            float u = x_in[(size_t)(t - 1) * D + i];
+            if (y) u = fmaf(sc, b2::ld(y + (size_t)(t - 1) * y_stride + i) + bi, u);
+            prow[i] = u;
+        }
+    }
+    if (!h) return;
+    __syncthreads();
+    const int Dg = D / groups;
+    group_inverse_rms(row, groups, Dg, eps, part_sm, ginv);
+    if (have_prev) group_inverse_rms(prow, groups, Dg, eps, part_sm, pinv);
+    const float* st = (shift_mu && li == 0 && ctx > 0 && slot >= 0) ? shift_state + (size_t)slot * D : nullptr;
+    T* ho = h + (size_t)t * h_stride;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        float v = row[i] * ginv[i / Dg] * norm_w[i];
+        if (shift_mu) {
+            float pv = 0.f;
+            if (have_prev) pv = prow[i] * pinv[i / Dg] * norm_w[i];
+            else if (st) pv = st[i];
+            v = fmaf(pv - v, shift_mu[i], v);
+        }
+        b2::st(ho + i, v);
+    }
+}
+
+__global__ void __launch_bounds__(kNormThreads)
+shift_state_kernel(const float* __restrict__ x, int D, const float* __restrict__ norm_w, int groups, float eps,
+                   const int32_t* __restrict__ cu_q, const int32_t* __restrict__ ctx_start,
+                   const int32_t* __restrict__ state_slot, float* __restrict__ shift_state) {
+    extern __shared__ __align__(16) float gn_sm[];   // row [D] | parts | ginv
+    float* row = gn_sm;
+    float* part_sm = gn_sm + D;
+    float* ginv = part_sm + groups * kNormWarps;
+    const int seq = blockIdx.x;
+    const int slot = state_slot[seq];
+    const int n = cu_q[seq + 1] - cu_q[seq];
+    if (ctx_start[seq] < 0 || slot < 0 || n <= 0) return;
+    const float* xt = x + (size_t)(cu_q[seq + 1] - 1) * D;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) row[i] = xt[i];
+    __syncthreads();
+    const int Dg = D / groups;
+    group_inverse_rms(row, groups, Dg, eps, part_sm, ginv);
+    float* st = shift_state + (size_t)slot * D;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) st[i] = row[i] * ginv[i / Dg] * norm_w[i];
+}
+
+}  // namespace
+
+extern "C" int b2_embed_sinusoid_norm(float* x, const void* embed, int act_dtype, const int64_t* tokens,
+                                      const int32_t* positions, int T, int D, const double* freq, const float* norm_w,
+                                      int groups, float eps, void* stream) {
+    B2_REQUIRE(T >= 0 && D > 0 && groups >= 1 && D % groups == 0, B2_EINVAL, "embed_sinusoid_norm: bad sizes D=%d groups=%d", D,
+               groups);
+    if (T == 0) return B2_OK;
+    B2_REQUIRE(x && embed && tokens && positions && freq, B2_EINVAL, "embed_sinusoid_norm: null pointer");
+    const size_t smem = ((size_t)D + (size_t)groups * (kNormWarps + 1)) * sizeof(float);
+    B2_REQUIRE(smem <= 200 * 1024, B2_EUNSUPPORTED, "embed_sinusoid_norm: width %d does not fit shared memory", D);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    B2_DISPATCH_ACT(act_dtype, A, {
+        auto kern = embed_sinusoid_norm_kernel<A>;
+        if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        kern<<<T, kNormThreads, smem, st>>>(x, static_cast<const A*>(embed), tokens, positions, D, freq, norm_w, groups, eps);
+    });
+    B2_CUDA_OK(cudaGetLastError());
+    return B2_OK;
+}
+
+extern "C" int b2_group_norm_step(const float* x_in, float* x_out, int T, int D, const void* y, int64_t y_stride,
+                                  const float* y_scale, const float* y_bias, const float* norm_w, int groups, float eps,
+                                  const float* shift_mu, const float* shift_state, const int32_t* cu_q,
+                                  const int32_t* ctx_start, const int32_t* state_slot, int n_seq, void* h, int64_t h_stride,
+                                  int act_dtype, void* stream) {
+    B2_REQUIRE(T >= 0 && D > 0 && groups >= 1 && D % groups == 0, B2_EINVAL, "group_norm_step: bad sizes D=%d groups=%d", D, groups);
+    if (T == 0 || (!y && !h && x_out == x_in)) return B2_OK;
+    B2_REQUIRE(x_in, B2_EINVAL, "group_norm_step: null residual");
+    B2_REQUIRE(!h || norm_w, B2_EINVAL, "group_norm_step: a read-out needs its norm weight");
+    B2_REQUIRE(!y || x_out, B2_EINVAL, "group_norm_step: a sublayer output needs a residual to land in");
+    B2_REQUIRE(!shift_mu || (h && cu_q && ctx_start && state_slot && shift_state && n_seq > 0), B2_EINVAL,
+               "group_norm_step: a token shift needs the read-out, the sequences and the state");
+    B2_REQUIRE(!(shift_mu && y && x_out == x_in), B2_EINVAL,
+               "group_norm_step: with a sublayer output and a token shift the residual cannot be updated in place");
+    const size_t smem = ((shift_mu ? 2 : 1) * (size_t)D + (size_t)groups * (kNormWarps + 2)) * sizeof(float);
+    B2_REQUIRE(smem <= 200 * 1024, B2_EUNSUPPORTED, "group_norm_step: width %d does not fit shared memory", D);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    B2_DISPATCH_ACT(act_dtype, A, {
+        auto kern = group_norm_step_kernel<A>;
+        if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        kern<<<T, kNormThreads, smem, st>>>(x_in, x_out, D, static_cast<const A*>(y), y_stride, y_scale, y_bias, norm_w, groups, eps,
+                                           shift_mu, shift_state, cu_q, ctx_start, state_slot, n_seq, static_cast<A*>(h), h_stride);
+    });
+    B2_CUDA_OK(cudaGetLastError());
+    return B2_OK;
+}
+
+extern "C" int b2_shift_state(const float* x, int D, const float* norm_w, int groups, float eps, const int32_t* cu_q,
+                              const int32_t* ctx_start, const int32_t* state_slot, int n_seq, float* shift_state, void* stream) {
+    B2_REQUIRE(D > 0 && groups >= 1 && D % groups == 0 && n_seq >= 0, B2_EINVAL, "shift_state: bad sizes D=%d groups=%d", D, groups);
+    if (n_seq == 0) return B2_OK;
+    B2_REQUIRE(x && norm_w && cu_q && ctx_start && state_slot && shift_state, B2_EINVAL, "shift_state: null pointer");
+    const size_t smem = ((size_t)D + (size_t)groups * (kNormWarps + 1)) * sizeof(float);
+    B2_REQUIRE(smem <= 200 * 1024, B2_EUNSUPPORTED, "shift_state: width %d does not fit shared memory", D);
+    if (smem > 48 * 1024)
+        B2_CUDA_OK(cudaFuncSetAttribute(shift_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    shift_state_kernel<<<n_seq, kNormThreads, smem, static_cast<cudaStream_t>(stream)>>>(x, D, norm_w, groups, eps, cu_q, ctx_start,
+                                                                                        state_slot, shift_state);
+    B2_CUDA_OK(cudaGetLastError());
+    return B2_OK;
+}

@@ -3,13 +3,19 @@
 //   b2_moe_route     z = W_r h in fp32 (one warp per token).  B2_ROUTE_TOPK_SOFTMAX: the `top` largest of z + b (lowest index
 //                    wins a tie), weights = softmax over the chosen logits only.  B2_ROUTE_SOFTMAX_ALL: s = softmax(z) over
 //                    all experts, the `top` largest of s + b are chosen, weights = their s (not renormalised).
+//                    B2_ROUTE_SIGMOID_GROUPED: s = sigmoid(z); the choice looks at c = s + b; the experts form `n_groups` equal
+//                    groups of neighbours, a group's score is the sum of its two largest c, and only experts of the
+//                    `keep_groups` best groups can be chosen (the others count as -inf); weights = the chosen s divided by
+//                    their sum (+ 1e-20), times `weight_scale`.  (b2_moe_route_ex / b2_moe_select_ex carry the three
+//                    parameters; n_groups = 1 is the ungrouped case.)
 //   b2_moe_select    the same choice from fp32 logits computed elsewhere (a library GEMM over a prompt batch).
 //   b2_moe_align     counting sort of the T*top (token, choice) pairs by expert into row tiles of kMoeBM rows: every tile
 //                    belongs to one expert, experts are padded to a tile boundary with -1.  Entirely on the device (no host
 //                    read of the counts), so the step stays capturable in a CUDA graph and never waits for the GPU.
 //   b2_moe_gate_up   per tile: act = glu(h W_gate[e]^T, h W_up[e]^T), rows gathered through the sorted list.  glu(g, u) is
 //                    SiLU(g) * u (B2_GLU_SILU) or, with g' = min(g, limit) and u' = clamp(u, -limit, limit),
-//                    g' * sigmoid(alpha * g') * (u' + 1) (B2_GLU_CLAMPED).
+//                    g' * sigmoid(alpha * g') * (u' + 1) (B2_GLU_CLAMPED).  B2_FF_RELU_SQ: experts without a gate,
+//                    act = max(h W_up[e]^T, 0)^2 (w_gate is not read).
 //   b2_moe_down      per tile: rows = act W_down[e]^T, fp32.
 //   b2_moe_combine   y[t] = sum_j weight[t, j] * rows[place of (t, j)], summed in choice order in fp32: a token's result
 //                    does not depend on what else is in the batch.
@@ -26,8 +32,79 @@ constexpr int kMoeBM = 32, kMoeBN = 64, kMoeBK = 32;
 
 // ------------------------------------------------------------------------------------------------- router
 // One warp picks the `top` experts of token t from its fp32 logits z [E] in shared memory (overwritten).
-__device__ __forceinline__ void route_select(float* z, int t, int E, int top, int scoring, const float* __restrict__ bias,
+struct RouteSpec {
+    int scoring, n_groups, keep_groups;
+    float weight_scale;
+};
+
+// floats of scratch per token beside its E logits
+__host__ __device__ __forceinline__ int route_scratch(int scoring, int E) { return scoring == B2_ROUTE_SIGMOID_GROUPED ? 2 * E : 0; }
+
+// lowest index wins a tie; every lane returns the winner
+__device__ __forceinline__ int warp_argmax(const float* c, int E, int lane, float& best_out) {
+    float best = -INFINITY;
+    int arg = 0x7fffffff;
+    for (int e = lane; e < E; e += 32)
+        if (c[e] > best) { best = c[e]; arg = e; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+        if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+    }
+    best_out = best;
+    return arg;
+}
+
+__device__ __forceinline__ void route_select(float* z, int t, int E, int top, RouteSpec rs, const float* __restrict__ bias,
                                              int lane, int32_t* __restrict__ ids, float* __restrict__ wts) {
+    const int scoring = rs.scoring;
+    if (scoring == B2_ROUTE_SIGMOID_GROUPED) {
+        float* c = z + E;                            // choice scores; then the group scores
+        float* gs = z + 2 * E;
+        for (int e = lane; e < E; e += 32) {
+            z[e] = b2::sigmoid_f(z[e]);
+            c[e] = z[e] + (bias ? bias[e] : 0.f);
+        }
+        __syncwarp();
+        const int ng = rs.n_groups;
+        if (ng > 1) {
+            const int per = E / ng;
+            for (int g = lane; g < ng; g += 32) {    // sum of the two largest choice scores of the group
+                float a = -INFINITY, b = -INFINITY;
+                for (int i = 0; i < per; ++i) {
+                    const float v = c[g * per + i];
+                    if (v > a) { b = a; a = v; } else if (v > b) { b = v; }
+                }
+                gs[g] = per > 1 ? a + b : a;
+            }
+            __syncwarp();
+            for (int g = lane; g < ng; g += 32) {    // a group is kept when fewer than keep_groups groups come before it
+                int before = 0;
+                for (int o = 0; o < ng; ++o) before += (gs[o] > gs[g] || (gs[o] == gs[g] && o < g)) ? 1 : 0;
+                if (before >= rs.keep_groups)
+                    for (int i = 0; i < per; ++i) c[g * per + i] = -INFINITY;
+            }
+            __syncwarp();
+        }
+        float sum = 0.f;
+        for (int j = 0; j < top; ++j) {
+            float best;
+            int arg = warp_argmax(c, E, lane, best);
+            if (arg == 0x7fffffff) arg = 0;
+            const float w = best == -INFINITY ? 0.f : z[arg];
+            sum += w;
+            if (lane == 0) {
+                ids[(size_t)t * top + j] = arg;
+                wts[(size_t)t * top + j] = w;
+                c[arg] = -INFINITY;
+            }
+            __syncwarp();
+        }
+        const float inv = rs.weight_scale / (sum + 1e-20f);
+        for (int j = lane; j < top; j += 32) wts[(size_t)t * top + j] *= inv;
+        return;
+    }
     if (scoring == B2_ROUTE_SOFTMAX_ALL) {
         // scores over all experts; the choice adds the correction, the weight is the plain score
         float mx = -INFINITY;
@@ -93,9 +170,11 @@ __device__ __forceinline__ void route_select(float* z, int t, int E, int top, in
 // divides the L2 traffic of a prompt batch by TOK), then warp t picks the `top` largest of token t.
 template <typename T, int TOK>
 __global__ void moe_route_kernel(const T* __restrict__ h, int64_t h_stride, const T* __restrict__ w_r,
-                                 const float* __restrict__ bias, int rows, int D, int E, int top, int scoring, bool vec,
+                                 const float* __restrict__ bias, int rows, int D, int E, int top, RouteSpec rs, bool vec,
                                  bool vec16, int32_t* __restrict__ ids, float* __restrict__ wts) {
-    extern __shared__ float route_sm[];              // h [TOK][D] | z [TOK][E]
+    extern __shared__ float route_sm[];              // h [TOK][D] | z [TOK][E + scratch]
+    const int scoring = rs.scoring;
+    const int ZE = E + route_scratch(scoring, E);
     float* hs = route_sm;
     float* zs = route_sm + (size_t)TOK * D;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -151,25 +230,26 @@ __global__ void moe_route_kernel(const T* __restrict__ h, int64_t h_stride, cons
 #pragma unroll
         for (int tt = 0; tt < TOK; ++tt) {
             const float v = b2::warp_sum(a[tt][0] + a[tt][1]);
-            if (lane == 0) zs[tt * E + e] = v + ((bias && scoring == B2_ROUTE_TOPK_SOFTMAX) ? bias[e] : 0.f);
+            if (lane == 0) zs[tt * ZE + e] = v + ((bias && scoring == B2_ROUTE_TOPK_SOFTMAX) ? bias[e] : 0.f);
         }
     }
     __syncthreads();
-    for (int tt = wid; tt < nt; tt += nw) route_select(zs + (size_t)tt * E, t0 + tt, E, top, scoring, bias, lane, ids, wts);
+    for (int tt = wid; tt < nt; tt += nw) route_select(zs + (size_t)tt * ZE, t0 + tt, E, top, rs, bias, lane, ids, wts);
 }
 
 // The same choice from logits that a library GEMM has produced (prompt batches): a warp per token.
 __global__ void moe_select_kernel(const float* __restrict__ logits, int64_t stride, const float* __restrict__ bias, int rows, int E,
-                                  int top, int scoring, int32_t* __restrict__ ids, float* __restrict__ wts) {
-    extern __shared__ float route_sm[];              // z [warps][E]
+                                  int top, RouteSpec rs, int32_t* __restrict__ ids, float* __restrict__ wts) {
+    extern __shared__ float route_sm[];              // z [warps][E + scratch]
+    const int scoring = rs.scoring;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int t = blockIdx.x * (blockDim.x >> 5) + wid;
     if (t >= rows) return;
-    float* z = route_sm + (size_t)wid * E;
+    float* z = route_sm + (size_t)wid * (E + route_scratch(scoring, E));
     for (int e = lane; e < E; e += 32)
         z[e] = logits[(size_t)t * stride + e] + ((bias && scoring == B2_ROUTE_TOPK_SOFTMAX) ? bias[e] : 0.f);
     __syncwarp();
-    route_select(z, t, E, top, scoring, bias, lane, ids, wts);
+    route_select(z, t, E, top, rs, bias, lane, ids, wts);
 }
 
 // ------------------------------------------------------------------------------------------------- align
@@ -394,17 +474,17 @@ __device__ __forceinline__ void tile_product(FA a_row, FB0 b0_row, FB1 b1_row, i
     __syncthreads();
 }
 
-template <typename T>
+template <typename T, int NB>
 __global__ void __launch_bounds__(128)
 moe_gate_up_kernel(const T* __restrict__ h, int64_t h_stride, const T* __restrict__ w_gate, const T* __restrict__ w_up,
                    int64_t w13_expert_stride, const int32_t* __restrict__ sorted, const int32_t* __restrict__ tile_expert,
                    int top, int D, int F, bool vec, int glu, float alpha, float limit, T* __restrict__ act) {
-    __shared__ __align__(128) unsigned char sm[TileSmem<T, 2>::BYTES];
+    __shared__ __align__(128) unsigned char sm[TileSmem<T, NB>::BYTES];
     const float* c_sm = reinterpret_cast<const float*>(sm);
     const int e = tile_expert[blockIdx.x];
     if (e < 0) return;
     const int m0 = blockIdx.x * kMoeBM, n0 = blockIdx.y * kMoeBN;
-    const T* wg = w_gate + (size_t)e * w13_expert_stride;
+    const T* wg = (NB == 2 ? w_gate : w_up) + (size_t)e * w13_expert_stride;
     const T* wu = w_up + (size_t)e * w13_expert_stride;
     auto a_row = [&](int r) -> const T* {
         const int s = sorted[m0 + r];
@@ -412,12 +492,19 @@ moe_gate_up_kernel(const T* __restrict__ h, int64_t h_stride, const T* __restric
     };
     auto g_row = [&](int r) -> const T* { return n0 + r < F ? wg + (size_t)(n0 + r) * D : nullptr; };
     auto u_row = [&](int r) -> const T* { return n0 + r < F ? wu + (size_t)(n0 + r) * D : nullptr; };
-    tile_product<T, 2>(a_row, g_row, u_row, D, vec, sm);
+    if (NB == 2) tile_product<T, NB>(a_row, g_row, u_row, D, vec, sm);
+    else tile_product<T, NB>(a_row, u_row, u_row, D, vec, sm);
     for (int idx = threadIdx.x; idx < kMoeBM * kMoeBN; idx += blockDim.x) {
         const int r = idx / kMoeBN, c = idx % kMoeBN;
         if (n0 + c < F && sorted[m0 + r] >= 0) {
-            const float g = c_sm[idx], u = c_sm[kMoeBM * kMoeBN + idx];
-            b2::st(act + (size_t)(m0 + r) * F + n0 + c, glu == B2_GLU_CLAMPED ? b2::glu_clamped_f(g, u, alpha, limit) : b2::silu_f(g) * u);
+            float v;
+            if (NB == 1) {
+                v = b2::relu_sq_f(c_sm[idx]);
+            } else {
+                const float g = c_sm[idx], u = c_sm[(NB - 1) * kMoeBM * kMoeBN + idx];
+                v = glu == B2_GLU_CLAMPED ? b2::glu_clamped_f(g, u, alpha, limit) : b2::silu_f(g) * u;
+            }
+            b2::st(act + (size_t)(m0 + r) * F + n0 + c, v);
         }
     }
 }
@@ -481,16 +568,32 @@ extern "C" int b2_moe_capacity(int n, int E) {
     return (n + used * (kMoeBM - 1) + kMoeBM - 1) / kMoeBM * kMoeBM;
 }
 
+static bool route_spec_ok(int scoring, int E, int top, int n_groups, int keep_groups) {
+    if (scoring == B2_ROUTE_TOPK_SOFTMAX || scoring == B2_ROUTE_SOFTMAX_ALL) return true;
+    if (scoring != B2_ROUTE_SIGMOID_GROUPED) return false;
+    return n_groups >= 1 && E % n_groups == 0 && keep_groups >= 1 && keep_groups <= n_groups &&
+           (int64_t)keep_groups * (E / n_groups) >= top;
+}
+
 extern "C" int b2_moe_route(const void* h, int64_t h_stride, const void* w_router, const float* bias, int act_dtype, int T,
                             int D, int E, int top, int scoring, int32_t* ids, float* weights, void* stream) {
+    return b2_moe_route_ex(h, h_stride, w_router, bias, act_dtype, T, D, E, top, scoring, 1, 1, 1.f, ids, weights, stream);
+}
+
+extern "C" int b2_moe_route_ex(const void* h, int64_t h_stride, const void* w_router, const float* bias, int act_dtype, int T,
+                               int D, int E, int top, int scoring, int n_groups, int keep_groups, float weight_scale,
+                               int32_t* ids, float* weights, void* stream) {
     B2_REQUIRE(T >= 0 && D > 0 && E > 0 && top >= 1 && top <= E, B2_EINVAL, "moe_route: bad sizes D=%d E=%d top=%d", D, E, top);
-    B2_REQUIRE(scoring == B2_ROUTE_TOPK_SOFTMAX || scoring == B2_ROUTE_SOFTMAX_ALL, B2_EINVAL, "moe_route: unknown scoring %d",
-               scoring);
+    B2_REQUIRE(route_spec_ok(scoring, E, top, n_groups, keep_groups), B2_EINVAL,
+               "moe_route: scoring %d with %d groups of which %d are kept cannot choose %d of %d experts", scoring, n_groups,
+               keep_groups, top, E);
     if (T == 0) return B2_OK;
     B2_REQUIRE(h && w_router && ids && weights, B2_EINVAL, "moe_route: null pointer");
+    const RouteSpec rs{scoring, n_groups, keep_groups, weight_scale};
+    const int ZE = E + route_scratch(scoring, E);
     // prompt batches: four tokens share a CTA (and every weight load); small batches keep a CTA per token
-    const int tok = (T >= 1024 && (size_t)4 * (D + E) * sizeof(float) <= 96 * 1024) ? 4 : 1;
-    const size_t smem = (size_t)tok * (D + E) * sizeof(float);
+    const int tok = (T >= 1024 && (size_t)4 * (D + ZE) * sizeof(float) <= 96 * 1024) ? 4 : 1;
+    const size_t smem = (size_t)tok * (D + ZE) * sizeof(float);
     B2_REQUIRE(smem <= 200 * 1024, B2_EUNSUPPORTED, "moe_route: width %d and %d experts do not fit shared memory", D, E);
     const int warps = E < 8 ? (E < 4 ? 4 : E) : 8;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -501,12 +604,12 @@ extern "C" int b2_moe_route(const void* h, int64_t h_stride, const void* w_route
             auto kern = moe_route_kernel<A, 4>;
             if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             kern<<<(T + 3) / 4, warps * 32, smem, st>>>(static_cast<const A*>(h), h_stride, static_cast<const A*>(w_router), bias,
-                                                        T, D, E, top, scoring, vec, vec16, ids, weights);
+                                                        T, D, E, top, rs, vec, vec16, ids, weights);
         } else {
             auto kern = moe_route_kernel<A, 1>;
             if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             kern<<<T, warps * 32, smem, st>>>(static_cast<const A*>(h), h_stride, static_cast<const A*>(w_router), bias, T, D, E, top,
-                                              scoring, vec, vec16, ids, weights);
+                                              rs, vec, vec16, ids, weights);
         }
     });
     B2_CUDA_OK(cudaGetLastError());
@@ -515,16 +618,23 @@ extern "C" int b2_moe_route(const void* h, int64_t h_stride, const void* w_route
 
 extern "C" int b2_moe_select(const float* logits, int64_t stride, const float* bias, int T, int E, int top, int scoring,
                              int32_t* ids, float* weights, void* stream) {
+    return b2_moe_select_ex(logits, stride, bias, T, E, top, scoring, 1, 1, 1.f, ids, weights, stream);
+}
+
+extern "C" int b2_moe_select_ex(const float* logits, int64_t stride, const float* bias, int T, int E, int top, int scoring,
+                                int n_groups, int keep_groups, float weight_scale, int32_t* ids, float* weights, void* stream) {
     B2_REQUIRE(T >= 0 && E > 0 && top >= 1 && top <= E && stride >= E, B2_EINVAL, "moe_select: bad sizes E=%d top=%d", E, top);
-    B2_REQUIRE(scoring == B2_ROUTE_TOPK_SOFTMAX || scoring == B2_ROUTE_SOFTMAX_ALL, B2_EINVAL, "moe_select: unknown scoring %d",
-               scoring);
+    B2_REQUIRE(route_spec_ok(scoring, E, top, n_groups, keep_groups), B2_EINVAL,
+               "moe_select: scoring %d with %d groups of which %d are kept cannot choose %d of %d experts", scoring, n_groups,
+               keep_groups, top, E);
     if (T == 0) return B2_OK;
     B2_REQUIRE(logits && ids && weights, B2_EINVAL, "moe_select: null pointer");
     const int warps = 4;
-    const size_t smem = (size_t)warps * E * sizeof(float);
+    const size_t smem = (size_t)warps * (E + route_scratch(scoring, E)) * sizeof(float);
     B2_REQUIRE(smem <= 48 * 1024, B2_EUNSUPPORTED, "moe_select: %d experts do not fit shared memory", E);
+    const RouteSpec rs{scoring, n_groups, keep_groups, weight_scale};
     moe_select_kernel<<<(T + warps - 1) / warps, warps * 32, smem, static_cast<cudaStream_t>(stream)>>>(logits, stride, bias, T, E, top,
-                                                                                                     scoring, ids, weights);
+                                                                                                     rs, ids, weights);
     B2_CUDA_OK(cudaGetLastError());
     return B2_OK;
 }
@@ -548,21 +658,28 @@ extern "C" int b2_moe_experts(const void* h, int64_t h_stride, const void* w_gat
                               const int32_t* tile_expert, const int32_t* place, const float* weights, void* act, float* rows,
                               void* y, int64_t y_stride, int glu, float glu_alpha, float glu_limit, void* stream) {
     B2_REQUIRE(T >= 0 && D > 0 && F > 0 && top >= 1 && cap % kMoeBM == 0, B2_EINVAL, "moe_experts: bad sizes");
-    B2_REQUIRE(glu == B2_GLU_SILU || glu == B2_GLU_CLAMPED, B2_EINVAL, "moe_experts: unknown gated activation %d", glu);
+    B2_REQUIRE(glu == B2_GLU_SILU || glu == B2_GLU_CLAMPED || glu == B2_FF_RELU_SQ, B2_EINVAL,
+               "moe_experts: unknown expert activation %d", glu);
     if (T == 0) return B2_OK;
-    B2_REQUIRE(h && w_gate && w_up && w_down && sorted && tile_expert && place && weights && act && rows && y, B2_EINVAL,
+    const bool gated = glu != B2_FF_RELU_SQ;
+    B2_REQUIRE(h && (w_gate || !gated) && w_up && w_down && sorted && tile_expert && place && weights && act && rows && y, B2_EINVAL,
                "moe_experts: null pointer");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int tiles = cap / kMoeBM;
     const int ve = act_dtype == B2_ACT_BF16 ? 8 : 4;
     B2_REQUIRE(w13_expert_stride >= (int64_t)F * D, B2_EINVAL, "moe_experts: expert stride below F*D");
     const bool vec1 = D % ve == 0 && h_stride % ve == 0 && w13_expert_stride % ve == 0 && b2_aligned16(h) &&
-                      b2_aligned16(w_gate) && b2_aligned16(w_up);
+                      (!gated || b2_aligned16(w_gate)) && b2_aligned16(w_up);
     const bool vec2 = F % ve == 0 && b2_aligned16(act) && b2_aligned16(w_down);
     B2_DISPATCH_ACT(act_dtype, A, {
-        moe_gate_up_kernel<A><<<dim3(tiles, (F + kMoeBN - 1) / kMoeBN), 128, 0, st>>>(
-            static_cast<const A*>(h), h_stride, static_cast<const A*>(w_gate), static_cast<const A*>(w_up), w13_expert_stride,
-            sorted, tile_expert, top, D, F, vec1, glu, glu_alpha, glu_limit, static_cast<A*>(act));
+        if (gated)
+            moe_gate_up_kernel<A, 2><<<dim3(tiles, (F + kMoeBN - 1) / kMoeBN), 128, 0, st>>>(
+                static_cast<const A*>(h), h_stride, static_cast<const A*>(w_gate), static_cast<const A*>(w_up), w13_expert_stride,
+                sorted, tile_expert, top, D, F, vec1, glu, glu_alpha, glu_limit, static_cast<A*>(act));
+        else
+            moe_gate_up_kernel<A, 1><<<dim3(tiles, (F + kMoeBN - 1) / kMoeBN), 128, 0, st>>>(
+                static_cast<const A*>(h), h_stride, nullptr, static_cast<const A*>(w_up), w13_expert_stride, sorted, tile_expert,
+                top, D, F, vec1, glu, glu_alpha, glu_limit, static_cast<A*>(act));
         moe_down_kernel<A><<<dim3(tiles, (D + kMoeBN - 1) / kMoeBN), 128, 0, st>>>(
             static_cast<const A*>(act), static_cast<const A*>(w_down), sorted, tile_expert, D, F, vec2, rows);
         moe_combine_kernel<A, float><<<T, 256, 0, st>>>(rows, place, weights, top, D, static_cast<A*>(y), y_stride);

@@ -11,6 +11,9 @@
 //   b2_relu_sq         out = max(in, 0)^2
 //   b2_glu_and_mul     out[t, i] = glu(in[t, i], in[t, I + i]) for rows [gate | up]: SiLU(g) * u (B2_GLU_SILU) or the bounded
 //                      unit g' * sigmoid(alpha g') * (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit) (B2_GLU_CLAMPED)
+//                      or gelu_tanh(g) * u, gelu_tanh(z) = z/2 (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))) (B2_GLU_GELU_TANH)
+//   b2_gate_mul        out[t, i] = x[t, i] * act(gate[t, i]) * scale with act = sigmoid (B2_GATE_SIGMOID) or SiLU
+//                      (B2_GATE_SILU): an output gate on concatenated head outputs, the three rows with strides of their own
 //   b2_softcap         z <- cap * tanh(z / cap) in place
 // The residual and all statistics are fp32 whatever the activation type.
 #include "b2_act.cuh"
@@ -122,7 +125,22 @@ __global__ void glu_and_mul_kernel(T* __restrict__ out, int64_t out_stride, cons
     const T* r = in + (size_t)t * in_stride;
     for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < I; i += gridDim.y * blockDim.x) {
         const float g = b2::ld(r + i), u = b2::ld(r + I + i);
-        b2::st(out + (size_t)t * out_stride + i, glu == B2_GLU_CLAMPED ? b2::glu_clamped_f(g, u, alpha, limit) : b2::silu_f(g) * u);
+        float v;
+        if (glu == B2_GLU_CLAMPED) v = b2::glu_clamped_f(g, u, alpha, limit);
+        else if (glu == B2_GLU_GELU_TANH) v = b2::gelu_tanh_f(g) * u;
+        else v = b2::silu_f(g) * u;
+        b2::st(out + (size_t)t * out_stride + i, v);
+    }
+}
+
+template <typename T>
+__global__ void gate_mul_kernel(T* __restrict__ out, int64_t out_stride, const T* __restrict__ x, int64_t x_stride,
+                                const T* __restrict__ gate, int64_t gate_stride, int I, int kind, float scale) {
+    const int t = blockIdx.x;
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < I; i += gridDim.y * blockDim.x) {
+        const float z = b2::ld(gate + (size_t)t * gate_stride + i);
+        const float g = kind == B2_GATE_SIGMOID ? b2::sigmoid_f(z) : b2::silu_f(z);
+        b2::st(out + (size_t)t * out_stride + i, b2::ld(x + (size_t)t * x_stride + i) * g * scale);
     }
 }
 
@@ -194,12 +212,27 @@ extern "C" int b2_relu_sq(void* out, int64_t out_stride, const void* in, int64_t
 extern "C" int b2_glu_and_mul(void* out, int64_t out_stride, const void* gate_up, int64_t in_stride, int act_dtype, int T, int I,
                               int glu, float alpha, float limit, void* stream) {
     B2_REQUIRE(T >= 0 && I > 0, B2_EINVAL, "glu_and_mul: bad sizes T=%d I=%d", T, I);
-    B2_REQUIRE(glu == B2_GLU_SILU || glu == B2_GLU_CLAMPED, B2_EINVAL, "glu_and_mul: unknown gated activation %d", glu);
+    B2_REQUIRE(glu == B2_GLU_SILU || glu == B2_GLU_CLAMPED || glu == B2_GLU_GELU_TANH, B2_EINVAL,
+               "glu_and_mul: unknown gated activation %d", glu);
     if (T == 0) return B2_OK;
     B2_REQUIRE(out && gate_up, B2_EINVAL, "glu_and_mul: null pointer");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     B2_DISPATCH_ACT(act_dtype, A, (glu_and_mul_kernel<A><<<rows_grid(I, T), 256, 0, st>>>(
         static_cast<A*>(out), out_stride, static_cast<const A*>(gate_up), in_stride, I, glu, alpha, limit)));
+    B2_CUDA_OK(cudaGetLastError());
+    return B2_OK;
+}
+
+extern "C" int b2_gate_mul(void* out, int64_t out_stride, const void* x, int64_t x_stride, const void* gate, int64_t gate_stride,
+                           int act_dtype, int T, int I, int kind, float scale, void* stream) {
+    B2_REQUIRE(T >= 0 && I > 0, B2_EINVAL, "gate_mul: bad sizes T=%d I=%d", T, I);
+    B2_REQUIRE(kind == B2_GATE_SILU || kind == B2_GATE_SIGMOID, B2_EINVAL, "gate_mul: unknown gate %d", kind);
+    if (T == 0) return B2_OK;
+    B2_REQUIRE(out && x && gate, B2_EINVAL, "gate_mul: null pointer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    B2_DISPATCH_ACT(act_dtype, A, (gate_mul_kernel<A><<<rows_grid(I, T), 256, 0, st>>>(
+        static_cast<A*>(out), out_stride, static_cast<const A*>(x), x_stride, static_cast<const A*>(gate), gate_stride, I, kind,
+        scale)));
     B2_CUDA_OK(cudaGetLastError());
     return B2_OK;
 }
