@@ -1,6 +1,7 @@
-"""`bench.py --family kofadra|gatolix`: prefill and decode throughput of a model family at layer sizes of real models
+"""`bench.py --family kofadra|gatolix|tonilix`: prefill and decode throughput of a model family at layer sizes of real models
 (random weights), beside the Llama model of equal width, heads, head size and ACTIVE feed-forward width, plus the device
-time of every kernel of the family with the roofline that bounds it beside the like kernel of the Llama path.
+time of every kernel of the family with the roofline that bounds it beside the like kernel of the Llama path (Tonilix:
+beside the Kofadra family, whose recurrent mixer, attention without rotation and routed experts are the closest).
 
 Both models run through the same engine (LLMEngine.replay_step: scheduler, pools, state slots, CUDA-graph decode).
   prefill   one prompt chunk of T tokens in one step; wall clock around the step (it ends with a stream synchronize)
@@ -318,10 +319,145 @@ def _kernels_gatolix(size, s, B, ctx, T):
         torch.cuda.empty_cache()
 
 
+def _kernels_tonilix(size, s, B, ctx, T):
+    """Device time of the Tonilix kernels and of the like Kofadra kernels on the same shapes."""
+    import torch
+    from b200attn import ops
+    dev = torch.device("cuda", 0)
+    HBM, TF, src = _peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    D, H, G, d, F, E, top, R = s["hidden"], s["heads"], s["kv_heads"], s["head_dim"], s["ff"], s["experts"], s["top"], 64
+    bf = torch.bfloat16
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)          # noqa: E731
+
+    def line(kernel, phase, ms, bytes_=0, flops=0, like=None):
+        gbs, tfs = bytes_ / ms / 1e6, flops / ms / 1e9
+        _emit(bench="kernel", size=size, kernel=kernel, phase=phase, ms=round(ms, 4), gb_per_s=round(gbs, 1),
+              tflop_per_s=round(tfs, 2), frac_hbm=round(gbs / HBM, 3), frac_bf16=round(tfs / TF, 4), peaks=src, like=like)
+
+    for phase, n_seq, q_len, c in (("prefill", 1, T, 0), ("decode", B, 1, ctx)):
+        rows = n_seq * q_len
+        nb_seq = (c + q_len + 15) // 16
+        tables = torch.arange(n_seq * nb_seq, dtype=torch.int32, device=dev).view(n_seq, nb_seq)
+        batch = ops.SeqBatch(i32([i * q_len for i in range(n_seq + 1)]), i32([c] * n_seq), tables, i32(list(range(n_seq))),
+                             n_seq, rows)
+        pos = (torch.arange(rows, device=dev) % q_len + c).to(torch.int32)
+        slots = (torch.arange(rows, device=dev) // q_len * (nb_seq * 16) + pos).to(torch.int64)
+        # ---- embedding with positions + norm  |  like: Kofadra's embedding into the streams
+        emb = torch.randn(s["vocab"], D, device=dev).to(bf)
+        tok = torch.randint(0, s["vocab"], (rows,), device=dev)
+        freq, nw = ops.sinusoid_frequencies(D, device=dev), torch.ones(D, device=dev)
+        ms = _time(lambda: ops.embed_sinusoid_norm(emb, tok, pos, freq, nw, 8, 1e-6), flush)
+        line("embed_sinusoid_norm", phase, ms, bytes_=rows * D * (2 + 4), like="embed_streams")
+        ms = _time(lambda: ops.embed_streams(emb, tok, 1, 1.0), flush)
+        line("embed_streams (Kofadra, 1 stream)", phase, ms, bytes_=rows * D * (2 + 4))
+        # ---- residual + scale + norm in groups (+ token shift)  |  like: Kofadra's stream step with one stream
+        x, x2 = torch.randn(rows, D, device=dev), torch.empty(rows, D, device=dev)
+        y = torch.randn(rows, D, device=dev).to(bf)
+        ls, mu = torch.ones(D, device=dev), torch.full((D,), 0.3, device=dev)
+        sst = torch.zeros(n_seq, D, device=dev)
+        ms = _time(lambda: ops.group_norm_step(x, y, ls, None, nw, 8, 1e-6, h_dtype=bf), flush)
+        line("group_norm_step (scale + norm in 8 groups)", phase, ms, bytes_=rows * D * (4 + 4 + 2 + 2), like="hc_step")
+        ms = _time(lambda: ops.group_norm_step(x, y, ls, None, nw, 8, 1e-6, h_dtype=bf, shift_mu=mu, shift_state=sst, batch=batch,
+                                               x_out=x2), flush)
+        line("group_norm_step (+ token shift and its state)", phase, ms, bytes_=rows * D * (4 + 4 + 2 + 2), like="hc_step")
+        xs = torch.randn(rows, 1, D, device=dev)
+        one = torch.ones(1, device=dev)
+        ms = _time(lambda: ops.hc_step(xs, y, None, one, one, nw, 1e-6, ops.NORM_RMS, h_dtype=bf), flush)
+        line("hc_step (Kofadra, 1 fp32 stream, RMS)", phase, ms, bytes_=rows * D * (4 + 4 + 2 + 2))
+        # ---- attention: query temperature + pool write  |  like: Kofadra's per-head norm + pool write; the attention kernel is shared
+        kc = torch.randn(n_seq * nb_seq, G, 16, d, device=dev).to(bf)
+        vc = torch.randn(n_seq * nb_seq, G, 16, d, device=dev).to(bf)
+        qkv = torch.randn(rows, (H + 2 * G) * d, device=dev).to(bf)
+        ms = _time(lambda: ops.qk_prep_cache(qkv, H, G, d, d, slots, kc, vc, pos, 0.25, 512), flush)
+        line("qk_prep_cache (query temperature + pool write)", phase, ms, bytes_=rows * (2 * H + 4 * G) * d * 2, like="qknorm_cache")
+        ms = _time(lambda: ops.qknorm_cache(qkv, H, G, d, d, nw[:d].contiguous(), nw[:d].contiguous(), 1e-6, slots, kc, vc), flush)
+        line("qknorm_cache (Kofadra)", phase, ms, bytes_=rows * (2 * H + 4 * G) * d * 2)
+        q = torch.randn(rows, H, d, device=dev).to(bf)
+        ms = _time(lambda: ops.chunk_attention(q, kc, vc, batch, d ** -0.5), flush)
+        if phase == "prefill":
+            line("chunk_attention (plain causal)", phase, ms, flops=4 * (T * (T + 1) // 2) * H * d, like="chunk_attention (Kofadra)")
+            ms = _time(lambda: ops.chunk_attention(q, kc, vc, batch, d ** -0.5, 1024, sink=1.0), flush)
+            pairs = sum(min(p % 1024, p) + 1 for p in range(T))
+            line("chunk_attention (Kofadra: blocks of 1024, sink)", phase, ms, flops=4 * pairs * H * d)
+        else:
+            line("chunk_attention (plain causal)", phase, ms, bytes_=n_seq * (c + 1) * G * 2 * d * 2, like="chunk_attention (Kofadra)")
+            ms = _time(lambda: ops.chunk_attention(q, kc, vc, batch, d ** -0.5, 1024, sink=1.0), flush)
+            line("chunk_attention (Kofadra: blocks of 1024, sink)", phase, ms, bytes_=n_seq * ((c % 1024) + 1) * G * 2 * d * 2)
+        o = torch.randn(rows, H * d, device=dev).to(bf)
+        gate = torch.randn(rows, H * d, device=dev).to(bf)
+        ms = _time(lambda: ops.gate_mul(o, gate, ops.GATE_SIGMOID, 1.2), flush)
+        line("gate_mul (sigmoid output gate)", phase, ms, bytes_=rows * H * d * 6, like="silu_and_mul")
+        gu = torch.randn(rows, 2 * H * d, device=dev).to(bf)
+        ms = _time(lambda: ops.silu_and_mul(gu), flush)
+        line("silu_and_mul (Llama)", phase, ms, bytes_=rows * H * d * 6)
+        # ---- recurrences with a decay per channel  |  like: Kofadra's delta rule with a decay per head
+        C = 2 * G * d + H * d
+        proj = torch.randn(rows, C + H * d + 2 * H, device=dev).to(bf)
+        a = torch.randn(rows, H * d, device=dev)
+        conv_w, A, dtb = torch.randn(C, 4, device=dev) * 0.5, -torch.ones(H, device=dev), torch.zeros(H * d, device=dev)
+        cstate = torch.zeros(n_seq, 3, C, dtype=bf, device=dev)
+        state = torch.zeros(n_seq, H, d, d, device=dev)
+        prep = lambda: ops.recur_prep(proj, H, G, d, d, batch, taps=4, conv_w=conv_w, conv_state=cstate, conv_silu=True, unit=True,  # noqa: E731
+                                      q_scale=d ** -0.5, off_beta=C, decay_mode=ops.DECAY_CHANNEL_SOFTPLUS, a=a, A_log=A, decay_bias=dtb)
+        ms = _time(prep, flush)
+        line("recur_prep (conv + unit vectors + decay per channel)", phase, ms, bytes_=rows * (C * 2 + C * 4 + H * d * 8 + 4 * H),
+             like="delta_prep")
+        dth = torch.zeros(H, device=dev)
+        ms = _time(lambda: ops.delta_prep(proj, C + H * d, C + H * d + H, H, G, d, d, 4, conv_w, A, dth, batch, cstate), flush)
+        line("delta_prep (Kofadra, decay per head)", phase, ms, bytes_=rows * (C * 2 + C * 4 + 8 * H))
+        qkv32, beta, decay = prep()
+        ms = _time(lambda: ops.channel_scan(qkv32, beta, decay, H, G, d, d, batch, state, delta=True), flush)
+        line("channel_scan (delta rule, decay per channel)", phase, ms, flops=8 * rows * H * d * d,
+             bytes_=n_seq * H * d * d * 4 * 2 + rows * (C + 2 * H * d) * 4, like="delta_scan")
+        Hr = max(H // 2, 1)
+        Cr = 3 * Hr * d
+        qr, dr_ = torch.randn(rows, Cr, device=dev), torch.rand(rows, Hr * d, device=dev)
+        st_r = torch.zeros(n_seq, Hr, d, d, device=dev)
+        ms = _time(lambda: ops.channel_scan(qr, None, dr_, Hr, Hr, d, d, batch, st_r, delta=False), flush)
+        line("channel_scan (gated linear attention, half the heads)", phase, ms, flops=6 * rows * Hr * d * d,
+             bytes_=n_seq * Hr * d * d * 4 * 2 + rows * (Cr + 2 * Hr * d) * 4, like="delta_scan")
+        _, beta_h, decay_h = ops.delta_prep(proj, C + H * d, C + H * d + H, H, G, d, d, 4, conv_w, A, dth, batch, cstate)
+        ms = _time(lambda: ops.delta_scan(qkv32, beta_h, decay_h, H, G, d, d, batch, state), flush)
+        line("delta_scan (Kofadra, decay per head)", phase, ms, flops=6 * rows * H * d * d,
+             bytes_=n_seq * H * d * d * 4 * 2 + rows * (C + H * d) * 4)
+        o32 = torch.randn(rows, H, d, device=dev)
+        ms = _time(lambda: ops.gated_head_norm(o32, gate, nw[:d].contiguous(), 1e-6, ops.GATE_SIGMOID), flush)
+        line("gated_head_norm (sigmoid gate)", phase, ms, bytes_=rows * H * d * (4 + 2 + 2), like="delta_out")
+        ms = _time(lambda: ops.delta_out(o32, proj, C, nw[:d].contiguous(), 1e-6), flush)
+        line("delta_out (Kofadra)", phase, ms, bytes_=rows * H * d * (4 + 2 + 2))
+        # ---- feed-forwards  |  like: Kofadra's router and gated experts; the Llama gated unit
+        act_in = torch.randn(rows, 2 * top * F, device=dev).to(bf)
+        ms = _time(lambda: ops.glu_and_mul(act_in, ops.GLU_GELU_TANH), flush)
+        line("glu_and_mul (gelu_tanh)", phase, ms, bytes_=rows * top * F * 6, like="silu_and_mul")
+        ms = _time(lambda: ops.silu_and_mul(act_in), flush)
+        line("silu_and_mul (Llama, feed-forward width)", phase, ms, bytes_=rows * top * F * 6)
+        h = torch.randn(rows, D, device=dev).to(bf)
+        wr, rb = (torch.randn(E, D, device=dev) * D ** -0.5).to(bf), torch.zeros(E, device=dev)
+        route = lambda: ops.moe_route(h, wr, rb, top, ops.ROUTE_SIGMOID_GROUPED, 8, 4, 2.0)          # noqa: E731
+        ms = _time(route, flush)
+        line("moe_route (sigmoid scores, 4 of 8 groups)", phase, ms, bytes_=rows * D * 2 + E * D * 2, flops=2 * rows * E * D, like="moe_route")
+        ms = _time(lambda: ops.moe_route(h, wr, rb, top), flush)
+        line("moe_route (Kofadra, softmax over the chosen)", phase, ms, bytes_=rows * D * 2 + E * D * 2, flops=2 * rows * E * D)
+        ids, wts = route()
+        wgu = (torch.randn(E, 2 * F, D, device=dev) * D ** -0.5).to(bf)
+        wup = wgu[:, :F].contiguous()
+        wd = (torch.randn(E, D, F, device=dev) * F ** -0.5).to(bf)
+        used = min(E, rows * top)
+        path = "vendor grouped GEMM" if rows * top >= ops.MOE_GROUPED_GEMM_MIN_PAIRS else "own tiled kernels"
+        ms = _time(lambda: ops.moe_experts(h, ids, wts, None, wup, wd, glu=ops.FF_RELU_SQ), flush)
+        line(f"moe_experts, ungated squared ReLU (sort + 2 grouped products + combine; {path})", phase, ms,
+             bytes_=used * 2 * F * D * 2, flops=4 * rows * top * F * D, like="moe_experts (Kofadra)")
+        ms = _time(lambda: ops.moe_experts(h, ids, wts, wgu[:, :F], wgu[:, F:], wd, w_gate_up=wgu), flush)
+        line(f"moe_experts (Kofadra, gated; {path})", phase, ms, bytes_=used * 3 * F * D * 2, flops=6 * rows * top * F * D)
+        del wgu, wup, wd, kc, vc, state, st_r, emb
+        torch.cuda.empty_cache()
+
+
 def run(family: str, sizes, steps: int, kernels: bool = True) -> None:
     import torch
     from b200attn.model import ModelConfig
-    if family not in ("kofadra", "gatolix"):
+    if family not in ("kofadra", "gatolix", "tonilix"):
         raise SystemExit(f"unknown family {family!r}")
     B, ctx, T = 64, 2560, 4096          # ctx: 2.5 mask blocks / windows of the bench geometries
     for name in sizes:
@@ -330,6 +466,11 @@ def run(family: str, sizes, steps: int, kernels: bool = True) -> None:
             s = SIZES[name]
             fcfg = bench_config(s["hidden"], s["layers"], s["heads"], s["kv_heads"], s["head_dim"], s["ff"], s["experts"],
                                 s["top"], s["vocab"], name=f"kofadra-{name}")
+        elif family == "tonilix":
+            from b200attn.tonilix import bench_config
+            s = SIZES[name]
+            fcfg = bench_config(s["hidden"], s["layers"], s["heads"], s["kv_heads"], s["head_dim"], s["ff"], s["experts"],
+                                s["top"], s["vocab"], name=f"tonilix-{name}")
         else:
             from b200attn.gatolix import bench_config
             s = GATOLIX_SIZES[name]
@@ -340,7 +481,12 @@ def run(family: str, sizes, steps: int, kernels: bool = True) -> None:
         _emit(bench="config", size=name, **s, **{f"{family}_params": fcfg.params}, llama_params=lcfg.params, prefill_tokens=T,
               decode_batch=B, decode_ctx=ctx, data="synthetic", dtype="bf16")
         _throughput(fcfg.name, fcfg, B, ctx, T, steps)
+        if family == "tonilix":                 # the closest family at equal size: plain residual, delta and attention layers
+            from b200attn.kofadra import bench_config as kofadra_config
+            kcfg = kofadra_config(s["hidden"], s["layers"], s["heads"], s["kv_heads"], s["head_dim"], s["ff"], s["experts"],
+                                  s["top"], s["vocab"], streams=0, name=f"kofadra-{name}")
+            _throughput(kcfg.name, kcfg, B, ctx, T, steps)
         _throughput(lcfg.name, lcfg, B, ctx, T, steps)
         if kernels:
-            (_kernels_kofadra if family == "kofadra" else _kernels_gatolix)(name, s, B, ctx, T)
+            {"kofadra": _kernels_kofadra, "gatolix": _kernels_gatolix, "tonilix": _kernels_tonilix}[family](name, s, B, ctx, T)
         torch.cuda.empty_cache()

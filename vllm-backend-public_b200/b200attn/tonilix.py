@@ -25,6 +25,7 @@ ranks of the low-rank projections from the tensors' shapes; weights from its *.s
 from __future__ import annotations
 
 import json
+import os
 import struct
 from dataclasses import dataclass
 from pathlib import Path
@@ -320,6 +321,10 @@ class TonilixModel:
         self.alloc_cache(num_blocks)
         self.alloc_state(max_num_seqs)
         self._arange = torch.arange(max_num_seqs + 1, dtype=torch.int32, device=device)
+        # the two halves of a parallel mixer are independent between the fused projection and the output projection: the
+        # recurrent half (few CTAs, a long dependent chain per sequence) runs on a second stream under the attention
+        self.overlap = os.environ.get("B2_PARALLEL_MIXER_STREAMS", "1") != "0"
+        self._side = torch.cuda.Stream(device)
         self.capture: Optional[list] = None         # tests: set to a list to collect the residual after every layer
 
     # ------------------------------------------------------------------ weights
@@ -533,20 +538,31 @@ class TonilixModel:
         proj = torch.nn.functional.linear(h, w[p + ".wproj"], w[p + ".bproj"])
         nl, nr = a.heads * a.vdim, b.heads * b.vdim
         cat = torch.empty(T, nl + nr, dtype=h.dtype, device=h.device)       # [left heads, gated | right heads, normed and gated]
+
+        def right():                                 # gated linear attention over the state slots
+            z = self._low_rank(proj[:, cols["a1"]:cols["a1"] + _pad8(b.decay_rank)], w[p + ".mix.right.a2"], True)
+            qkv, _, decay = ops.recur_prep(proj[:, cols["right"]:], b.heads, b.heads, b.dim, b.vdim, batch, q_scale=b.dim ** -0.5,
+                                           decay_mode=ops.DECAY_CHANNEL_SIGMOID_POW, a=z, decay_bias=w[p + ".mix.right.a2.b"],
+                                           tau=b.tau)
+            s = ops.channel_scan(qkv, None, decay, b.heads, b.heads, b.dim, b.vdim, batch, self.state[li], delta=False)
+            ops.gated_head_norm(s, proj[:, cols["rgate"]:cols["rgate"] + nr], w[p + ".mix.right.norm"], self.cfg.eps,
+                                ops.GATE_SILU, m.right_scale, out=cat[:, nl:])
+
+        main = torch.cuda.current_stream(self.dev)
+        if self.overlap:
+            self._side.wait_stream(main)             # proj and cat exist
+            with torch.cuda.stream(self._side):
+                right()
         # softmax attention over the paged pools
         wl = a.heads * a.dim + a.kv_heads * (a.dim + a.vdim)
         q = ops.qk_prep_cache(proj[:, :wl], a.heads, a.kv_heads, a.dim, a.vdim, slots, self.k_cache[li], self.v_cache[li],
                               positions, a.temp_coef, a.temp_every)
         o = ops.chunk_attention(q, self.k_cache[li], self.v_cache[li], batch, a.scale)
         ops.gate_mul(o.view(T, nl), proj[:, cols["lgate"]:cols["lgate"] + nl], ops.GATE_SIGMOID, m.left_scale, out=cat[:, :nl])
-        # gated linear attention over the state slots
-        z = self._low_rank(proj[:, cols["a1"]:cols["a1"] + _pad8(b.decay_rank)], w[p + ".mix.right.a2"], True)
-        qkv, _, decay = ops.recur_prep(proj[:, cols["right"]:], b.heads, b.heads, b.dim, b.vdim, batch, q_scale=b.dim ** -0.5,
-                                       decay_mode=ops.DECAY_CHANNEL_SIGMOID_POW, a=z, decay_bias=w[p + ".mix.right.a2.b"],
-                                       tau=b.tau)
-        s = ops.channel_scan(qkv, None, decay, b.heads, b.heads, b.dim, b.vdim, batch, self.state[li], delta=False)
-        ops.gated_head_norm(s, proj[:, cols["rgate"]:cols["rgate"] + nr], w[p + ".mix.right.norm"], self.cfg.eps, ops.GATE_SILU,
-                            m.right_scale, out=cat[:, nl:])
+        if self.overlap:
+            main.wait_stream(self._side)
+        else:
+            right()
         return torch.nn.functional.linear(cat, w[p + ".wo"])                # + left_scale * o.b, added with the residual
 
     def _mlp(self, li: int, h: torch.Tensor) -> torch.Tensor:

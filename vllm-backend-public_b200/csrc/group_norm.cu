@@ -91,56 +91,106 @@ embed_sinusoid_norm_kernel(float* __restrict__ x, const T* __restrict__ embed, c
     for (int i = threadIdx.x; i < D; i += blockDim.x) xt[i] = row[i] * ginv[i / Dg] * norm_w[i];
 }
 
-template <typename T>
+// W = 4: every access is a 16-byte (fp32) or 8-byte (bf16) vector; W = 1: any width and alignment.  A CTA walks
+// `rows_per_cta` consecutive rows: with a token shift the normalised row stays in shared memory as the next row's `prev`,
+// so only the first row of a CTA normalises its predecessor a second time (from that row's inputs, never from x_out).
+// A thread keeps to its own columns in every pass; only the group statistics look across threads.
+template <typename T, int W>
 __global__ void __launch_bounds__(kNormThreads)
-group_norm_step_kernel(const float* __restrict__ x_in, float* __restrict__ x_out, int D, const T* __restrict__ y, int64_t y_stride,
-                       const float* __restrict__ y_scale, const float* __restrict__ y_bias, const float* __restrict__ norm_w,
-                       int groups, float eps, const float* __restrict__ shift_mu, const float* __restrict__ shift_state,
+group_norm_step_kernel(const float* __restrict__ x_in, float* __restrict__ x_out, int rows, int rows_per_cta, int D,
+                       const T* __restrict__ y, int64_t y_stride, const float* __restrict__ y_scale,
+                       const float* __restrict__ y_bias, const float* __restrict__ norm_w, int groups, float eps,
+                       const float* __restrict__ shift_mu, const float* __restrict__ shift_state,
                        const int32_t* __restrict__ cu_q, const int32_t* __restrict__ ctx_start,
                        const int32_t* __restrict__ state_slot, int n_seq, T* __restrict__ h, int64_t h_stride) {
-    extern __shared__ __align__(16) float gn_sm[];   // row [D] | prev row [D] (shift) | parts | ginv | pinv
-    const int t = blockIdx.x;
-    float* row = gn_sm;
-    float* prow = gn_sm + D;
+    extern __shared__ __align__(16) float gn_sm[];   // row [D] | second row [D] (shift) | parts | ginv
+    float* cur = gn_sm;
+    float* prv = gn_sm + D;
     float* part_sm = gn_sm + (shift_mu ? 2 : 1) * (size_t)D;
     float* ginv = part_sm + groups * kNormWarps;
-    float* pinv = ginv + groups;
-    int li = 0, ctx = -1, slot = -1;
-    if (shift_mu) {
-        const int seq = b2::seq_of_row(cu_q, n_seq, t);
-        li = t - cu_q[seq];
-        ctx = ctx_start[seq];
-        slot = state_slot[seq];
-    }
-    const bool have_prev = shift_mu && li > 0 && ctx >= 0;
-    for (int i = threadIdx.x; i < D; i += blockDim.x) {
-        float v = x_in[(size_t)t * D + i];
-        const float sc = y_scale ? y_scale[i] : 1.f, bi = y_bias ? y_bias[i] : 0.f;
-        if (y) v = fmaf(sc, b2::ld(y + (size_t)t * y_stride + i) + bi, v);
-        row[i] = v;
-        if (x_out && (y || x_out != x_in)) x_out[(size_t)t * D + i] = v;
-        if (have_prev) {
-            float u = x_in[(size_t)(t - 1) * D + i];
-            if (y) u = fmaf(sc, b2::ld(y + (size_t)(t - 1) * y_stride + i) + bi, u);
-            prow[i] = u;
-        }
-    }
-    if (!h) return;
-    __syncthreads();
     const int Dg = D / groups;
-    group_inverse_rms(row, groups, Dg, eps, part_sm, ginv);
-    if (have_prev) group_inverse_rms(prow, groups, Dg, eps, part_sm, pinv);
-    const float* st = (shift_mu && li == 0 && ctx > 0 && slot >= 0) ? shift_state + (size_t)slot * D : nullptr;
-    T* ho = h + (size_t)t * h_stride;
-    for (int i = threadIdx.x; i < D; i += blockDim.x) {
-        float v = row[i] * ginv[i / Dg] * norm_w[i];
-        if (shift_mu) {
-            float pv = 0.f;
-            if (have_prev) pv = prow[i] * pinv[i / Dg] * norm_w[i];
-            else if (st) pv = st[i];
-            v = fmaf(pv - v, shift_mu[i], v);
+    const int step = blockDim.x * W;
+    const bool write_out = x_out && (y || x_out != x_in);
+    // x_in[t] + y_scale * (y[t] + y_bias) into dst; `store`: also into x_out
+    auto load_row = [&](int t, float* dst, bool store) {
+        for (int i = threadIdx.x * W; i < D; i += step) {
+            float v[4] = {0.f, 0.f, 0.f, 0.f};
+            if (W == 4) b2::ld4(x_in + (size_t)t * D + i, v); else v[0] = x_in[(size_t)t * D + i];
+            if (y) {
+                float u[4] = {0.f, 0.f, 0.f, 0.f}, sc[4] = {1.f, 1.f, 1.f, 1.f}, bi[4] = {0.f, 0.f, 0.f, 0.f};
+                if (W == 4) {
+                    b2::ld4(y + (size_t)t * y_stride + i, u);
+                    if (y_scale) b2::ld4(y_scale + i, sc);
+                    if (y_bias) b2::ld4(y_bias + i, bi);
+                } else {
+                    u[0] = b2::ld(y + (size_t)t * y_stride + i);
+                    if (y_scale) sc[0] = y_scale[i];
+                    if (y_bias) bi[0] = y_bias[i];
+                }
+#pragma unroll
+                for (int c = 0; c < W; ++c) v[c] = fmaf(sc[c], u[c] + bi[c], v[c]);
+            }
+#pragma unroll
+            for (int c = 0; c < W; ++c) dst[i + c] = v[c];
+            if (store) {
+                if (W == 4) b2::st4(x_out + (size_t)t * D + i, v); else x_out[(size_t)t * D + i] = v[0];
+            }
         }
-        b2::st(ho + i, v);
+    };
+    // dst <- dst / rms of its group * w, in place (own columns)
+    auto normalise = [&](float* dst) {
+        for (int i = threadIdx.x * W; i < D; i += step) {
+            float w[4] = {0.f, 0.f, 0.f, 0.f};
+            if (W == 4) b2::ld4(norm_w + i, w); else w[0] = norm_w[i];
+#pragma unroll
+            for (int c = 0; c < W; ++c) dst[i + c] = dst[i + c] * ginv[(i + c) / Dg] * w[c];
+        }
+    };
+    const int t0 = blockIdx.x * rows_per_cta, t1 = min(t0 + rows_per_cta, rows);
+    int seq = 0;
+    if (shift_mu) {
+        seq = b2::seq_of_row(cu_q, n_seq, t0);
+        if (t0 - cu_q[seq] > 0 && ctx_start[seq] >= 0) {         // the row before the CTA's first: normalised once more
+            load_row(t0 - 1, prv, false);
+            __syncthreads();
+            group_inverse_rms(prv, groups, Dg, eps, part_sm, ginv);
+            normalise(prv);
+        }
+    }
+    for (int t = t0; t < t1; ++t) {
+        load_row(t, cur, write_out);
+        if (!h) continue;
+        __syncthreads();
+        group_inverse_rms(cur, groups, Dg, eps, part_sm, ginv);
+        normalise(cur);
+        T* ho = h + (size_t)t * h_stride;
+        if (!shift_mu) {
+            for (int i = threadIdx.x * W; i < D; i += step) {
+                if (W == 4) b2::st4(ho + i, *reinterpret_cast<const float(*)[4]>(cur + i)); else b2::st(ho + i, cur[i]);
+            }
+            __syncthreads();                         // the statistics' readers are done before the next row lands
+            continue;
+        }
+        while (seq + 1 < n_seq && cu_q[seq + 1] <= t) ++seq;
+        const int li = t - cu_q[seq], ctx = ctx_start[seq], slot = state_slot[seq];
+        const float* pv = (li > 0 && ctx >= 0) ? prv : ((li == 0 && ctx > 0 && slot >= 0) ? shift_state + (size_t)slot * D : nullptr);
+        for (int i = threadIdx.x * W; i < D; i += step) {
+            float p[4] = {0.f, 0.f, 0.f, 0.f}, mu[4] = {0.f, 0.f, 0.f, 0.f}, o[4];
+            if (W == 4) {
+                if (pv) b2::ld4(pv + i, p);
+                b2::ld4(shift_mu + i, mu);
+            } else {
+                if (pv) p[0] = pv[i];
+                mu[0] = shift_mu[i];
+            }
+#pragma unroll
+            for (int c = 0; c < W; ++c) o[c] = fmaf(p[c] - cur[i + c], mu[c], cur[i + c]);
+            if (W == 4) b2::st4(ho + i, o); else b2::st(ho + i, o[0]);
+        }
+        __syncthreads();
+        float* sw = cur;                             // this row is the next one's `prev`
+        cur = prv;
+        prv = sw;
     }
 }
 
@@ -200,15 +250,28 @@ extern "C" int b2_group_norm_step(const float* x_in, float* x_out, int T, int D,
                "group_norm_step: a token shift needs the read-out, the sequences and the state");
     B2_REQUIRE(!(shift_mu && y && x_out == x_in), B2_EINVAL,
                "group_norm_step: with a sublayer output and a token shift the residual cannot be updated in place");
-    const size_t smem = ((shift_mu ? 2 : 1) * (size_t)D + (size_t)groups * (kNormWarps + 2)) * sizeof(float);
+    const size_t smem = ((shift_mu ? 2 : 1) * (size_t)D + (size_t)groups * (kNormWarps + 1)) * sizeof(float);
     B2_REQUIRE(smem <= 200 * 1024, B2_EUNSUPPORTED, "group_norm_step: width %d does not fit shared memory", D);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // long batches with a token shift: four rows a CTA, so that three of four rows find their predecessor in shared memory
+    const int per = (shift_mu && T >= 2048) ? 4 : 1;
+    const bool vec = D % 4 == 0 && b2_aligned16(x_in) && (!x_out || b2_aligned16(x_out)) &&
+                     (!y || (y_stride % 4 == 0 && b2_aligned16(y))) && (!h || (h_stride % 4 == 0 && b2_aligned16(h))) &&
+                     (!y_scale || b2_aligned16(y_scale)) && (!y_bias || b2_aligned16(y_bias)) && (!norm_w || b2_aligned16(norm_w)) &&
+                     (!shift_mu || (b2_aligned16(shift_mu) && b2_aligned16(shift_state)));
+#define B2_GROUP_NORM(W)                                                                                                    \
+    do {                                                                                                                    \
+        auto kern = group_norm_step_kernel<A, W>;                                                                           \
+        if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        kern<<<(T + per - 1) / per, kNormThreads, smem, st>>>(x_in, x_out, T, per, D, static_cast<const A*>(y), y_stride, y_scale, \
+                                                              y_bias, norm_w, groups, eps, shift_mu, shift_state, cu_q, ctx_start, \
+                                                              state_slot, n_seq, static_cast<A*>(h), h_stride);             \
+    } while (0)
     B2_DISPATCH_ACT(act_dtype, A, {
-        auto kern = group_norm_step_kernel<A>;
-        if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        kern<<<T, kNormThreads, smem, st>>>(x_in, x_out, D, static_cast<const A*>(y), y_stride, y_scale, y_bias, norm_w, groups, eps,
-                                           shift_mu, shift_state, cu_q, ctx_start, state_slot, n_seq, static_cast<A*>(h), h_stride);
+        if (vec) B2_GROUP_NORM(4);
+        else B2_GROUP_NORM(1);
     });
+#undef B2_GROUP_NORM
     B2_CUDA_OK(cudaGetLastError());
     return B2_OK;
 }

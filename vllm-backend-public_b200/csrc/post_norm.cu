@@ -118,29 +118,46 @@ __global__ void relu_sq_kernel(T* __restrict__ out, int64_t out_stride, const T*
     }
 }
 
-template <typename T>
+template <typename T, int W>
 __global__ void glu_and_mul_kernel(T* __restrict__ out, int64_t out_stride, const T* __restrict__ in, int64_t in_stride, int I,
                                    int glu, float alpha, float limit) {
     const int t = blockIdx.x;
     const T* r = in + (size_t)t * in_stride;
-    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < I; i += gridDim.y * blockDim.x) {
-        const float g = b2::ld(r + i), u = b2::ld(r + I + i);
-        float v;
-        if (glu == B2_GLU_CLAMPED) v = b2::glu_clamped_f(g, u, alpha, limit);
-        else if (glu == B2_GLU_GELU_TANH) v = b2::gelu_tanh_f(g) * u;
-        else v = b2::silu_f(g) * u;
-        b2::st(out + (size_t)t * out_stride + i, v);
+    for (int i = (blockIdx.y * blockDim.x + threadIdx.x) * W; i < I; i += gridDim.y * blockDim.x * W) {
+        float g[4] = {0.f, 0.f, 0.f, 0.f}, u[4] = {0.f, 0.f, 0.f, 0.f}, v[4];
+        if (W == 4) {
+            b2::ld4(r + i, g);
+            b2::ld4(r + I + i, u);
+        } else {
+            g[0] = b2::ld(r + i);
+            u[0] = b2::ld(r + I + i);
+        }
+#pragma unroll
+        for (int c = 0; c < W; ++c) {
+            if (glu == B2_GLU_CLAMPED) v[c] = b2::glu_clamped_f(g[c], u[c], alpha, limit);
+            else if (glu == B2_GLU_GELU_TANH) v[c] = b2::gelu_tanh_f(g[c]) * u[c];
+            else v[c] = b2::silu_f(g[c]) * u[c];
+        }
+        if (W == 4) b2::st4(out + (size_t)t * out_stride + i, v); else b2::st(out + (size_t)t * out_stride + i, v[0]);
     }
 }
 
-template <typename T>
+template <typename T, int W>
 __global__ void gate_mul_kernel(T* __restrict__ out, int64_t out_stride, const T* __restrict__ x, int64_t x_stride,
                                 const T* __restrict__ gate, int64_t gate_stride, int I, int kind, float scale) {
     const int t = blockIdx.x;
-    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < I; i += gridDim.y * blockDim.x) {
-        const float z = b2::ld(gate + (size_t)t * gate_stride + i);
-        const float g = kind == B2_GATE_SIGMOID ? b2::sigmoid_f(z) : b2::silu_f(z);
-        b2::st(out + (size_t)t * out_stride + i, b2::ld(x + (size_t)t * x_stride + i) * g * scale);
+    for (int i = (blockIdx.y * blockDim.x + threadIdx.x) * W; i < I; i += gridDim.y * blockDim.x * W) {
+        float z[4] = {0.f, 0.f, 0.f, 0.f}, a[4] = {0.f, 0.f, 0.f, 0.f}, v[4];
+        if (W == 4) {
+            b2::ld4(gate + (size_t)t * gate_stride + i, z);
+            b2::ld4(x + (size_t)t * x_stride + i, a);
+        } else {
+            z[0] = b2::ld(gate + (size_t)t * gate_stride + i);
+            a[0] = b2::ld(x + (size_t)t * x_stride + i);
+        }
+#pragma unroll
+        for (int c = 0; c < W; ++c) v[c] = a[c] * (kind == B2_GATE_SIGMOID ? b2::sigmoid_f(z[c]) : b2::silu_f(z[c])) * scale;
+        if (W == 4) b2::st4(out + (size_t)t * out_stride + i, v); else b2::st(out + (size_t)t * out_stride + i, v[0]);
     }
 }
 
@@ -217,8 +234,14 @@ extern "C" int b2_glu_and_mul(void* out, int64_t out_stride, const void* gate_up
     if (T == 0) return B2_OK;
     B2_REQUIRE(out && gate_up, B2_EINVAL, "glu_and_mul: null pointer");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    B2_DISPATCH_ACT(act_dtype, A, (glu_and_mul_kernel<A><<<rows_grid(I, T), 256, 0, st>>>(
-        static_cast<A*>(out), out_stride, static_cast<const A*>(gate_up), in_stride, I, glu, alpha, limit)));
+    const bool vec = I % 4 == 0 && in_stride % 4 == 0 && out_stride % 4 == 0 && b2_aligned16(gate_up) && b2_aligned16(out);
+    B2_DISPATCH_ACT(act_dtype, A, {
+        if (vec) glu_and_mul_kernel<A, 4><<<rows_grid(I / 4, T), 256, 0, st>>>(static_cast<A*>(out), out_stride,
+                                                                              static_cast<const A*>(gate_up), in_stride, I, glu,
+                                                                              alpha, limit);
+        else glu_and_mul_kernel<A, 1><<<rows_grid(I, T), 256, 0, st>>>(static_cast<A*>(out), out_stride,
+                                                                      static_cast<const A*>(gate_up), in_stride, I, glu, alpha, limit);
+    });
     B2_CUDA_OK(cudaGetLastError());
     return B2_OK;
 }
@@ -230,9 +253,15 @@ extern "C" int b2_gate_mul(void* out, int64_t out_stride, const void* x, int64_t
     if (T == 0) return B2_OK;
     B2_REQUIRE(out && x && gate, B2_EINVAL, "gate_mul: null pointer");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    B2_DISPATCH_ACT(act_dtype, A, (gate_mul_kernel<A><<<rows_grid(I, T), 256, 0, st>>>(
-        static_cast<A*>(out), out_stride, static_cast<const A*>(x), x_stride, static_cast<const A*>(gate), gate_stride, I, kind,
-        scale)));
+    const bool vec = I % 4 == 0 && x_stride % 4 == 0 && gate_stride % 4 == 0 && out_stride % 4 == 0 && b2_aligned16(x) &&
+                     b2_aligned16(gate) && b2_aligned16(out);
+    B2_DISPATCH_ACT(act_dtype, A, {
+        if (vec) gate_mul_kernel<A, 4><<<rows_grid(I / 4, T), 256, 0, st>>>(static_cast<A*>(out), out_stride, static_cast<const A*>(x),
+                                                                           x_stride, static_cast<const A*>(gate), gate_stride, I,
+                                                                           kind, scale);
+        else gate_mul_kernel<A, 1><<<rows_grid(I, T), 256, 0, st>>>(static_cast<A*>(out), out_stride, static_cast<const A*>(x),
+                                                                   x_stride, static_cast<const A*>(gate), gate_stride, I, kind, scale);
+    });
     B2_CUDA_OK(cudaGetLastError());
     return B2_OK;
 }
