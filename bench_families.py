@@ -376,12 +376,24 @@ def _kernels_tonilix(size, s, B, ctx, T):
         q = torch.randn(rows, H, d, device=dev).to(bf)
         ms = _time(lambda: ops.chunk_attention(q, kc, vc, batch, d ** -0.5), flush)
         if phase == "prefill":
-            line("chunk_attention (plain causal)", phase, ms, flops=4 * (T * (T + 1) // 2) * H * d, like="chunk_attention (Kofadra)")
+            line("chunk_attention (plain causal; heads of other sizes than 128)", phase, ms, flops=4 * (T * (T + 1) // 2) * H * d,
+                 like="chunk_attention (Kofadra)")
+            if d == 128:
+                cu, cs = i32([0, T]), i32([0])
+                ms = _time(lambda: ops.prefill_attention(q, kc, vc, tables, cu, cs, total_tokens=T), flush)
+                line("prefill_attention (heads of 128: the tcgen05 kernel of the Llama path)", phase, ms,
+                     flops=4 * (T * (T + 1) // 2) * H * d, like="chunk_attention (Kofadra)")
             ms = _time(lambda: ops.chunk_attention(q, kc, vc, batch, d ** -0.5, 1024, sink=1.0), flush)
             pairs = sum(min(p % 1024, p) + 1 for p in range(T))
             line("chunk_attention (Kofadra: blocks of 1024, sink)", phase, ms, flops=4 * pairs * H * d)
         else:
-            line("chunk_attention (plain causal)", phase, ms, bytes_=n_seq * (c + 1) * G * 2 * d * 2, like="chunk_attention (Kofadra)")
+            line("chunk_attention (plain causal; heads of other sizes than 128)", phase, ms, bytes_=n_seq * (c + 1) * G * 2 * d * 2,
+                 like="chunk_attention (Kofadra)")
+            if d == 128:
+                sl = i32([c + 1] * n_seq)
+                ms = _time(lambda: ops.paged_decode(q, kc, vc, tables, sl), flush)
+                line("paged_decode (heads of 128: the kernel of the Llama path)", phase, ms, bytes_=n_seq * (c + 1) * G * 2 * d * 2,
+                     like="chunk_attention (Kofadra)")
             ms = _time(lambda: ops.chunk_attention(q, kc, vc, batch, d ** -0.5, 1024, sink=1.0), flush)
             line("chunk_attention (Kofadra: blocks of 1024, sink)", phase, ms, bytes_=n_seq * ((c % 1024) + 1) * G * 2 * d * 2)
         o = torch.randn(rows, H * d, device=dev).to(bf)

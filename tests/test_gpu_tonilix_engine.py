@@ -18,7 +18,7 @@ import tonilix_util as U
 
 pytestmark = pytest.mark.gpu
 
-CONFIGS = {"a": U.cfg_a, "b": U.cfg_b, "c": U.cfg_c, "d": U.cfg_d, "e": U.cfg_e}
+CONFIGS = {"a": U.cfg_a, "b": U.cfg_b, "c": U.cfg_c, "d": U.cfg_d, "e": U.cfg_e, "f": U.cfg_f}
 
 
 @pytest.fixture(scope="module")
@@ -80,7 +80,7 @@ def test_portions_of_many_sizes(cuda, models, name):
 
 
 @pytest.mark.parametrize("name,dtype", [("a", "float32"), ("b", "float32"), ("c", "float32"), ("d", "float32"), ("e", "float32"),
-                                        ("a", "bfloat16"), ("c", "bfloat16"), ("e", "bfloat16")])
+                                        ("f", "float32"), ("a", "bfloat16"), ("c", "bfloat16"), ("e", "bfloat16"), ("f", "bfloat16")])
 def test_unequal_batches_with_reuse_of_pages_and_slots(cuda, models, name, dtype):
     """Up to four live requests, prompt portions beside single tokens; requests leave and new ones take over their pages
     and state slots (a pool of 15 pages for ~320 tokens in total).  Every request equals the oracle over its own tokens,
@@ -124,6 +124,26 @@ def test_long_decoding_through_graph_and_eager_steps(cuda, models, eager):
     got = U.replay(eng, reqs, sched)
     _check(got, cfg, W, reqs, "float32", "long decode")
     assert eng.stats.decode_steps >= 229 and (eager or len(eng._graphs) >= 2)
+    eng.close()
+
+
+def test_heads_of_128_take_the_llama_attention_kernels(cuda, models):
+    """bf16 with the full library: prompt chunks and decode rows of a parallel mixer with heads of 128 run on the tcgen05
+    prompt kernel and the paged-decode kernel; the logits equal those of the family's own attention kernel."""
+    from b200attn import _lib
+    cfg, W, path = models["f"]
+    reqs = {"p": U.tokens(150, cfg["vocab"], 1), "q": U.tokens(40, cfg["vocab"], 2)}
+    sched = [[("p", 100)], [("p", 1), ("q", 30)]] + [[("p", 1), ("q", 1)] for _ in range(10)] + [[("p", 39)]]
+    eng = U.make_engine(path, "bfloat16")
+    if not _lib.is_full():
+        pytest.skip("the core library has no paged-decode / tcgen05 kernels")
+    assert eng.model._llama_attention
+    fast = U.replay(eng, reqs, sched)
+    eng.model._llama_attention = False
+    eng._graphs.clear()
+    own = U.replay(eng, reqs, sched)
+    for rid in reqs:
+        assert U.rel_err(fast[rid], own[rid], "bfloat16") <= 2e-2
     eng.close()
 
 

@@ -73,6 +73,12 @@ def cfg_e():      # head sizes the tensor-core prompt kernel takes in bf16 (mult
                             parallel(attn(2, 1, 64, 32, 0.125, 0.25, 64), gla(4, 16, 64, 8.0), 1.0, 1.0, mlp=moe(4, 1, 48))], groups=4)
 
 
+def cfg_f():      # heads of 128 on the attention: in bf16 with the full library it runs on the Llama path's attention kernels
+    return config(128, 90, [parallel(attn(4, 2, 128, 128, 0.09, 0.6, 10), gla(2, 16, 32, 6.0), 1.3, 0.8, mlp=dense(96)),
+                            delta(2, 1, 16, 16, 3, moe(4, 2, 32, groups=2, keep=1, scale=1.5)),
+                            parallel(attn(2, 1, 128, 128, 0.05), gla(1, 32, 16, 12.0), mlp=moe(3, 1, 40))], groups=2)
+
+
 def strip(cfg: dict) -> dict:
     """The configuration as it is written to config.json: without the helper keys that size the random low-rank tensors."""
     import copy

@@ -150,6 +150,7 @@ SIGNATURES = {
 }
 
 _lib = None
+_partial = False
 
 
 def _not_built(name: str, path: Path):
@@ -161,7 +162,7 @@ def _not_built(name: str, path: Path):
 
 def load() -> C.CDLL:
     """Load the library once; raise loudly when it is absent or its ABI differs."""
-    global _lib
+    global _lib, _partial
     if _lib is not None:
         return _lib
     path, partial = LIB_PATH, False
@@ -186,8 +187,14 @@ def load() -> C.CDLL:
     v = lib.b2_version()
     if v != ABI_VERSION:
         raise ImportError(f"{LIB_PATH}: ABI version {v}, binding expects {ABI_VERSION}")
-    _lib = lib
+    _lib, _partial = lib, partial
     return lib
+
+
+def is_full() -> bool:
+    """True when the loaded library holds every entry point (the paged-decode and tcgen05 prompt kernels too)."""
+    load()
+    return not _partial
 
 
 def check(rc: int) -> None:

@@ -325,6 +325,11 @@ class TonilixModel:
         # recurrent half (few CTAs, a long dependent chain per sequence) runs on a second stream under the attention
         self.overlap = os.environ.get("B2_PARALLEL_MIXER_STREAMS", "1") != "0"
         self._side = torch.cuda.Stream(device)
+        # heads of 128 in bf16 are what the Llama path's attention kernels are built for (tcgen05 prompt chunks, TMA paged
+        # decode): a parallel mixer with such heads runs on them when the full library is loaded
+        from . import _lib
+        self._llama_attention = dtype == torch.bfloat16 and block_size in (8, 16, 32) and _lib.is_full() \
+            and os.environ.get("B2_TONILIX_LLAMA_ATTENTION", "1") != "0"
         self.capture: Optional[list] = None         # tests: set to a list to collect the residual after every layer
 
     # ------------------------------------------------------------------ weights
@@ -531,7 +536,7 @@ class TonilixModel:
         return torch.nn.functional.linear(out, w[p + ".mix.o"])
 
     def _parallel_mixer(self, li: int, h: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor,
-                        batch: ops.SeqBatch) -> torch.Tensor:
+                        batch: ops.SeqBatch, n_decode: int = 0, dec_bt=None, dec_sl=None, prefill=None) -> torch.Tensor:
         m, w, p, cols = self.cfg.layer_specs[li].mixer, self.w, f"l{li}", self.cols[li]
         a, b = m.left, m.right
         T = h.shape[0]
@@ -557,7 +562,15 @@ class TonilixModel:
         wl = a.heads * a.dim + a.kv_heads * (a.dim + a.vdim)
         q = ops.qk_prep_cache(proj[:, :wl], a.heads, a.kv_heads, a.dim, a.vdim, slots, self.k_cache[li], self.v_cache[li],
                               positions, a.temp_coef, a.temp_every)
-        o = ops.chunk_attention(q, self.k_cache[li], self.v_cache[li], batch, a.scale)
+        if self._llama_attention and a.dim == 128 and a.vdim == 128:
+            o = torch.empty(T, a.heads, 128, dtype=h.dtype, device=h.device)
+            if n_decode:
+                ops.paged_decode(q[:n_decode], self.k_cache[li], self.v_cache[li], dec_bt, dec_sl, scale=a.scale, out=o[:n_decode])
+            if prefill is not None and prefill.total_tokens:
+                ops.prefill_attention(q[n_decode:], self.k_cache[li], self.v_cache[li], prefill.block_tables, prefill.cu_q,
+                                      prefill.ctx_start, total_tokens=prefill.total_tokens, scale=a.scale, out=o[n_decode:])
+        else:
+            o = ops.chunk_attention(q, self.k_cache[li], self.v_cache[li], batch, a.scale)
         ops.gate_mul(o.view(T, nl), proj[:, cols["lgate"]:cols["lgate"] + nl], ops.GATE_SIGMOID, m.left_scale, out=cat[:, :nl])
         if self.overlap:
             main.wait_stream(self._side)
@@ -599,7 +612,8 @@ class TonilixModel:
             if isinstance(L.mixer, DeltaSpec):
                 y, ybias = self._delta_mixer(li, h, batch), None
             else:
-                y, ybias = self._parallel_mixer(li, h, positions, slots, batch), w[p + ".bo"]
+                y = self._parallel_mixer(li, h, positions, slots, batch, n_decode, dec_block_tables, dec_seq_lens, prefill)
+                ybias = w[p + ".bo"]
             scale = w[p + ".ls1"]
             if L.mlp is not None:
                 h = ops.group_norm_step(x, y, scale, ybias, w[p + ".norm2"], c.groups, c.eps, h_dtype=self.dtype)
