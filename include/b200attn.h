@@ -576,7 +576,9 @@ B2_API int b2_group_norm_step(const float* x_in, float* x_out, int T, int D, con
                               const float* y_scale, const float* y_bias, const float* norm_w, int groups, float eps,
                               const float* shift_mu /* or NULL */, const float* shift_state /* [slots, D] */,
                               const int32_t* cu_q, const int32_t* ctx_start, const int32_t* state_slot, int n_seq, void* h,
-                              int64_t h_stride, int act_dtype, void* stream);
+                              int64_t h_stride, int act_dtype,
+                              int advance_state /* 1: one row per sequence, the launch also does b2_shift_state's work */,
+                              void* stream);
 B2_API int b2_shift_state(const float* x, int D, const float* norm_w, int groups, float eps, const int32_t* cu_q,
                           const int32_t* ctx_start, const int32_t* state_slot, int n_seq, float* shift_state, void* stream);
 /* latent_attention.cu: attention over one shared low-rank latent + one shared rotated key part per token */

@@ -137,7 +137,7 @@ SIGNATURES = {
     "b2_glu_and_mul": (i32, [vp, i64, vp, i64, i32, i32, i32, i32, f32, f32, vp]),
     "b2_gate_mul": (i32, [vp, i64, vp, i64, vp, i64, i32, i32, i32, i32, f32, vp]),
     "b2_embed_sinusoid_norm": (i32, [vp, vp, i32, vp, vp, i32, i32, vp, vp, i32, f32, vp]),
-    "b2_group_norm_step": (i32, [vp, vp, i32, i32, vp, i64, vp, vp, vp, i32, f32, vp, vp, vp, vp, vp, i32, vp, i64, i32, vp]),
+    "b2_group_norm_step": (i32, [vp, vp, i32, i32, vp, i64, vp, vp, vp, i32, f32, vp, vp, vp, vp, vp, i32, vp, i64, i32, i32, vp]),
     "b2_shift_state": (i32, [vp, i32, vp, i32, f32, vp, vp, vp, i32, vp, vp]),
     "b2_softcap": (i32, [vp, i64, i32, i32, i32, f32, vp]),
     "b2_latent_prep": (i32, [vp, i64, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, f32, vp, vp, i32, vp, i32, vp, vp, vp]),

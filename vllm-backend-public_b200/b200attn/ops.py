@@ -1017,10 +1017,11 @@ def group_norm_step(x: torch.Tensor, y: Optional[torch.Tensor] = None, y_scale: 
             raise ValueError("with y and a token shift the residual is written to another buffer (x_out)")
         cu, ctx, slots, n_seq = batch.cu_q, batch.ctx_start, batch.state_slots, batch.n_seq
     act = _act(h if h is not None else y, "h / y") if (h is not None or y is not None) else ACT_BF16
+    single = shift_mu is not None and T == n_seq            # one row per sequence: the same launch advances the state
     _lib.check(lib.b2_group_norm_step(_ptr(x), _ptr(x_out), T, D, _ptr(y), ys, _ptr(y_scale), _ptr(y_bias), _ptr(norm_w),
                                       int(groups), float(eps), _ptr(shift_mu), _ptr(shift_state), _ptr(cu), _ptr(ctx),
-                                      _ptr(slots), n_seq, _ptr(h), D, act, _stream(dev)))
-    if shift_mu is not None:
+                                      _ptr(slots), n_seq, _ptr(h), D, act, int(single), _stream(dev)))
+    if shift_mu is not None and not single:
         _lib.check(lib.b2_shift_state(_ptr(x_out), D, _ptr(norm_w), int(groups), float(eps), _ptr(cu), _ptr(ctx), _ptr(slots),
                                       n_seq, _ptr(shift_state), _stream(dev)))
     return h

@@ -16,6 +16,9 @@
 //                            inputs, which must not have been overwritten).
 //   b2_shift_state           state[slot of sequence i] = gnorm(x[last row of sequence i]; w): what the next portion or
 //                            decode step of that sequence reads as `prev`.  Runs after b2_group_norm_step on the stream.
+//                            A batch of one row per sequence (a decode step) needs no second launch: with
+//                            `advance_state` b2_group_norm_step stores the row it has just normalised itself, since the
+//                            thread that read a column of the slot is the one that overwrites it.
 //   gnorm(v; w): v is cut into `groups` equal consecutive parts, each divided by sqrt(mean(part^2) + eps), times w.
 // The residual and all statistics are fp32 whatever the activation type.  Reductions run in a fixed order: a row's result
 // does not depend on the batch around it, and the in-kernel `prev` equals what b2_shift_state stores bit for bit.
@@ -102,7 +105,8 @@ group_norm_step_kernel(const float* __restrict__ x_in, float* __restrict__ x_out
                        const float* __restrict__ y_bias, const float* __restrict__ norm_w, int groups, float eps,
                        const float* __restrict__ shift_mu, const float* __restrict__ shift_state,
                        const int32_t* __restrict__ cu_q, const int32_t* __restrict__ ctx_start,
-                       const int32_t* __restrict__ state_slot, int n_seq, T* __restrict__ h, int64_t h_stride) {
+                       const int32_t* __restrict__ state_slot, int n_seq, T* __restrict__ h, int64_t h_stride,
+                       float* __restrict__ state_out) {
     extern __shared__ __align__(16) float gn_sm[];   // row [D] | second row [D] (shift) | parts | ginv
     float* cur = gn_sm;
     float* prv = gn_sm + D;
@@ -162,35 +166,44 @@ group_norm_step_kernel(const float* __restrict__ x_in, float* __restrict__ x_out
         if (!h) continue;
         __syncthreads();
         group_inverse_rms(cur, groups, Dg, eps, part_sm, ginv);
-        normalise(cur);
         T* ho = h + (size_t)t * h_stride;
-        if (!shift_mu) {
-            for (int i = threadIdx.x * W; i < D; i += step) {
-                if (W == 4) b2::st4(ho + i, *reinterpret_cast<const float(*)[4]>(cur + i)); else b2::st(ho + i, cur[i]);
-            }
-            __syncthreads();                         // the statistics' readers are done before the next row lands
-            continue;
+        const float* pv = nullptr;
+        float* keep = nullptr;                       // one row per sequence: the row's reader of the state also advances it
+        if (shift_mu) {
+            while (seq + 1 < n_seq && cu_q[seq + 1] <= t) ++seq;
+            const int li = t - cu_q[seq], ctx = ctx_start[seq], slot = state_slot[seq];
+            pv = (li > 0 && ctx >= 0) ? prv : ((li == 0 && ctx > 0 && slot >= 0) ? shift_state + (size_t)slot * D : nullptr);
+            if (state_out && ctx >= 0 && slot >= 0) keep = state_out + (size_t)slot * D;
         }
-        while (seq + 1 < n_seq && cu_q[seq + 1] <= t) ++seq;
-        const int li = t - cu_q[seq], ctx = ctx_start[seq], slot = state_slot[seq];
-        const float* pv = (li > 0 && ctx >= 0) ? prv : ((li == 0 && ctx > 0 && slot >= 0) ? shift_state + (size_t)slot * D : nullptr);
+        // one pass: normalise, keep the normalised row for the next row's blend, blend with the row before, store
         for (int i = threadIdx.x * W; i < D; i += step) {
-            float p[4] = {0.f, 0.f, 0.f, 0.f}, mu[4] = {0.f, 0.f, 0.f, 0.f}, o[4];
+            float w[4] = {0.f, 0.f, 0.f, 0.f}, p[4] = {0.f, 0.f, 0.f, 0.f}, mu[4] = {0.f, 0.f, 0.f, 0.f}, o[4];
             if (W == 4) {
+                b2::ld4(norm_w + i, w);
                 if (pv) b2::ld4(pv + i, p);
-                b2::ld4(shift_mu + i, mu);
+                if (shift_mu) b2::ld4(shift_mu + i, mu);
             } else {
+                w[0] = norm_w[i];
                 if (pv) p[0] = pv[i];
-                mu[0] = shift_mu[i];
+                if (shift_mu) mu[0] = shift_mu[i];
             }
 #pragma unroll
-            for (int c = 0; c < W; ++c) o[c] = fmaf(p[c] - cur[i + c], mu[c], cur[i + c]);
+            for (int c = 0; c < W; ++c) {
+                const float v = cur[i + c] * ginv[(i + c) / Dg] * w[c];
+                if (shift_mu) cur[i + c] = v;
+                o[c] = shift_mu ? fmaf(p[c] - v, mu[c], v) : v;
+            }
             if (W == 4) b2::st4(ho + i, o); else b2::st(ho + i, o[0]);
+            if (keep) {
+                if (W == 4) b2::st4(keep + i, *reinterpret_cast<const float(*)[4]>(cur + i)); else keep[i] = cur[i];
+            }
         }
-        __syncthreads();
-        float* sw = cur;                             // this row is the next one's `prev`
-        cur = prv;
-        prv = sw;
+        __syncthreads();                             // the statistics' readers are done before the next row lands
+        if (shift_mu) {
+            float* sw = cur;                         // this row is the next one's `prev`
+            cur = prv;
+            prv = sw;
+        }
     }
 }
 
@@ -240,7 +253,7 @@ extern "C" int b2_group_norm_step(const float* x_in, float* x_out, int T, int D,
                                   const float* y_scale, const float* y_bias, const float* norm_w, int groups, float eps,
                                   const float* shift_mu, const float* shift_state, const int32_t* cu_q,
                                   const int32_t* ctx_start, const int32_t* state_slot, int n_seq, void* h, int64_t h_stride,
-                                  int act_dtype, void* stream) {
+                                  int act_dtype, int advance_state, void* stream) {
     B2_REQUIRE(T >= 0 && D > 0 && groups >= 1 && D % groups == 0, B2_EINVAL, "group_norm_step: bad sizes D=%d groups=%d", D, groups);
     if (T == 0 || (!y && !h && x_out == x_in)) return B2_OK;
     B2_REQUIRE(x_in, B2_EINVAL, "group_norm_step: null residual");
@@ -248,13 +261,16 @@ extern "C" int b2_group_norm_step(const float* x_in, float* x_out, int T, int D,
     B2_REQUIRE(!y || x_out, B2_EINVAL, "group_norm_step: a sublayer output needs a residual to land in");
     B2_REQUIRE(!shift_mu || (h && cu_q && ctx_start && state_slot && shift_state && n_seq > 0), B2_EINVAL,
                "group_norm_step: a token shift needs the read-out, the sequences and the state");
+    B2_REQUIRE(!advance_state || (shift_mu && T == n_seq), B2_EINVAL,
+               "group_norm_step: the state is advanced in the same launch only for one row per sequence (%d rows, %d sequences)", T,
+               n_seq);
     B2_REQUIRE(!(shift_mu && y && x_out == x_in), B2_EINVAL,
                "group_norm_step: with a sublayer output and a token shift the residual cannot be updated in place");
     const size_t smem = ((shift_mu ? 2 : 1) * (size_t)D + (size_t)groups * (kNormWarps + 1)) * sizeof(float);
     B2_REQUIRE(smem <= 200 * 1024, B2_EUNSUPPORTED, "group_norm_step: width %d does not fit shared memory", D);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     // long batches with a token shift: four rows a CTA, so that three of four rows find their predecessor in shared memory
-    const int per = (shift_mu && T >= 2048) ? 4 : 1;
+    const int per = (shift_mu && T >= 2048) ? (T >= 8192 ? 8 : 4) : 1;
     const bool vec = D % 4 == 0 && b2_aligned16(x_in) && (!x_out || b2_aligned16(x_out)) &&
                      (!y || (y_stride % 4 == 0 && b2_aligned16(y))) && (!h || (h_stride % 4 == 0 && b2_aligned16(h))) &&
                      (!y_scale || b2_aligned16(y_scale)) && (!y_bias || b2_aligned16(y_bias)) && (!norm_w || b2_aligned16(norm_w)) &&
@@ -265,7 +281,8 @@ extern "C" int b2_group_norm_step(const float* x_in, float* x_out, int T, int D,
         if (smem > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
         kern<<<(T + per - 1) / per, kNormThreads, smem, st>>>(x_in, x_out, T, per, D, static_cast<const A*>(y), y_stride, y_scale, \
                                                               y_bias, norm_w, groups, eps, shift_mu, shift_state, cu_q, ctx_start, \
-                                                              state_slot, n_seq, static_cast<A*>(h), h_stride);             \
+                                                              state_slot, n_seq, static_cast<A*>(h), h_stride,              \
+                                                              advance_state ? const_cast<float*>(shift_state) : nullptr);   \
     } while (0)
     B2_DISPATCH_ACT(act_dtype, A, {
         if (vec) B2_GROUP_NORM(4);
