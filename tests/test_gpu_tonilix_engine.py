@@ -224,3 +224,53 @@ def test_trace_replay_program(cuda, models, tmp_path, dtype):
     got1 = torch.from_numpy(np.fromfile(out / "1.f32", dtype="<f4").reshape(2, -1))
     tol = U.TOL[dtype] * (1 if dtype == "float32" else 3)
     assert U.rel_err(got0, la[[0, 32]]) <= tol and U.rel_err(got1, torch.stack([la[33], lb[8]])) <= tol
+
+
+def test_server_serves_a_model_directory(cuda, models):
+    """`python -m b200attn.server --model DIR --dtype float32`: the family comes from config.json, completions are the
+    oracle's greedy continuation of a token-id prompt (a prompt whose six greedy steps all have a clear winner)."""
+    import socket
+    import time
+
+    import requests
+    cfg, W, path = models["b"]
+    sock = socket.socket()
+    sock.bind(("127.0.0.1", 0))
+    port = sock.getsockname()[1]
+    sock.close()
+    root = Path(__file__).resolve().parent.parent
+    env = dict(os.environ, PYTHONPATH=str(root / "vllm-backend-public_b200"))
+    proc = subprocess.Popen([sys.executable, "-m", "b200attn.server", "--model", str(path), "--dtype", "float32", "--port", str(port),
+                             "--host", "127.0.0.1", "--max-num-seqs", "4", "--max-model-len", "256",
+                             "--num-gpu-blocks-override", "80", "--served-model-name", "tonilix-test"], env=env,
+                            stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+    base = f"http://127.0.0.1:{port}"
+    try:
+        for _ in range(600):
+            if proc.poll() is not None:
+                raise RuntimeError("server exited: " + proc.stdout.read().decode()[-2000:])
+            try:
+                if requests.get(base + "/health", timeout=1).status_code == 200:
+                    break
+            except requests.RequestException:
+                pass
+            time.sleep(0.2)
+        else:
+            raise RuntimeError("server did not become healthy")
+        prompt = U.tokens(11, cfg["vocab"], 80)
+        r = requests.post(base + "/v1/completions", json={"model": "tonilix-test", "prompt": prompt, "max_tokens": 6,
+                                                          "temperature": 0.0, "ignore_eos": True}, timeout=60)
+        assert r.status_code == 200, r.text
+        body = r.json()
+        assert body["usage"]["prompt_tokens"] == 11 and body["usage"]["completion_tokens"] == 6
+        seq = list(prompt)
+        for _ in range(6):
+            seq.append(int(U.oracle_logits(cfg, W, seq)[-1].argmax()))
+        want = bytes(t % 256 for t in seq[11:]).decode("utf-8", errors="replace")      # the byte tokenizer's text
+        assert body["choices"][0]["text"] == want
+    finally:
+        proc.terminate()
+        try:
+            proc.wait(20)
+        except subprocess.TimeoutExpired:
+            proc.kill()
