@@ -36,7 +36,7 @@
 extern "C" {
 #endif
 
-#define B2_ABI_VERSION 4
+#define B2_ABI_VERSION 5
 
 #if defined(__GNUC__)
 #define B2_API __attribute__((visibility("default")))
@@ -499,6 +499,7 @@ B2_API int b2_delta_out(const float* o, const void* proj, int64_t proj_stride, i
 #define B2_DECAY_HEAD_SOFTPLUS        0   /* decay [T, H]      = exp(-exp(A_log[h]) softplus(proj[off_a + h] + bias[h])) */
 #define B2_DECAY_CHANNEL_SOFTPLUS     1   /* decay [T, H, dk]  = exp(-exp(A_log[h]) softplus(a[h, i] + bias[h, i])) */
 #define B2_DECAY_CHANNEL_SIGMOID_POW  2   /* decay [T, H, dk]  = sigmoid(a[h, i] + bias[h, i]) ^ (1 / tau) */
+#define B2_DECAY_HEAD_CONST           3   /* decay [T, H]      = decay_bias[h]: one fixed number per head */
 #define B2_GATE_SILU    0
 #define B2_GATE_SIGMOID 1
 B2_API int b2_recur_prep(const void* proj, int64_t proj_stride, int act_dtype, int T, int H, int G, int dk, int dv,
@@ -526,6 +527,22 @@ B2_API int b2_chunk_attention(void* out, const void* q, const void* k_cache, con
                               const int32_t* block_tables, int max_nb, const int32_t* cu_q, const int32_t* ctx_start,
                               int n_seq, int T, int H, int G, int dk, int dv, int bs, float scale, int chunk, float sink,
                               float sink_logit, void* stream);
+/* b2_chunk_attention with every mask and epilogue parameter: a sliding window that keeps the sequence's first tokens
+ * (position i sees j <= i with i - j < window or j < keep_first; window = 0: none), the sink's logit per query head
+ * (sink_logits [H] fp32, or NULL: sink_logit for all), a sigmoid gate per (token, head) on the output (gate rows of the
+ * activation type with gate_stride elements between tokens, or NULL). */
+B2_API int b2_masked_attention(void* out, const void* q, const void* k_cache, const void* v_cache, int act_dtype,
+                               const int32_t* block_tables, int max_nb, const int32_t* cu_q, const int32_t* ctx_start,
+                               int n_seq, int T, int H, int G, int dk, int dv, int bs, float scale, int chunk, int window,
+                               int keep_first, float sink, float sink_logit, const float* sink_logits, const void* gate,
+                               int64_t gate_stride, void* stream);
+/* rows [q (H*dk) | k (G*dk)] or [q | k | v (G*dv)]: the first rot_dims entries of every q and k head turn by the token's
+ * position (pairs (i, i + rot_dims/2), or (2i, 2i+1) when interleaved; cos_sin fp32 [max_pos, rot_dims] = cos | sin
+ * halves), q -> q_out [T, H, dk], rotated k -> K pool; the V pool gets v, or with v_from_k the k heads BEFORE the rotation. */
+B2_API int b2_qk_rope_cache(const void* qkv, int64_t qkv_stride, int act_dtype, int T, int H, int G, int dk, int dv,
+                            int v_from_k, int rot_dims, int interleaved, const int32_t* positions, const float* cos_sin,
+                            int max_pos, const int64_t* slots, int bs, void* q_out, void* k_cache, void* v_cache,
+                            void* stream);
 B2_API int b2_moe_tile_rows(void);
 B2_API int b2_moe_capacity(int n, int E);
 #define B2_ROUTE_TOPK_SOFTMAX 0   /* top-k of logits + bias, weights = softmax over the chosen logits */
@@ -560,6 +577,8 @@ B2_API int b2_moe_experts(const void* h, int64_t h_stride, const void* w_gate, c
 B2_API int b2_sandwich_norm(float* x, int T, int D, const void* y, int64_t y_stride, const float* post_w,
                             const float* post_b, const float* pre_w, const float* pre_b, float eps, int norm_kind, void* h,
                             int64_t h_stride, int act_dtype, void* stream);
+B2_API int b2_row_norm(void* out, int64_t out_stride, const void* in, int64_t in_stride, int act_dtype, int T, int n,
+                       const float* w /* [n] or NULL */, float eps, void* stream);
 B2_API int b2_relu_sq(void* out, int64_t out_stride, const void* in, int64_t in_stride, int act_dtype, int T, int I,
                       void* stream);
 B2_API int b2_glu_and_mul(void* out, int64_t out_stride, const void* gate_up, int64_t in_stride, int act_dtype, int T, int I,
@@ -586,6 +605,12 @@ B2_API int b2_latent_prep(const void* proj, int64_t proj_stride, int act_dtype, 
                           int R, int q_off, int dkv_off /* < 0: the layer reads another layer's pool */, const float* norm_w,
                           float eps, const int32_t* positions, const float* cos_sin, int max_pos, const int64_t* slots, int bs,
                           void* qa, void* cache, void* stream);
+/* b2_latent_prep with the query heads (rows q, from column q_off) and the down-projection (rows kv, from column dkv_off) in
+ * two buffers */
+B2_API int b2_latent_prep_rows(const void* q, int64_t q_stride, const void* kv, int64_t kv_stride, int act_dtype, int T, int H,
+                               int dn, int dr, int rot_dims, int R, int q_off, int dkv_off, const float* norm_w, float eps,
+                               const int32_t* positions, const float* cos_sin, int max_pos, const int64_t* slots, int bs,
+                               void* qa, void* cache, void* stream);
 B2_API int b2_latent_attention(void* out, const void* qa, const void* cache, int act_dtype, const int32_t* block_tables,
                                int max_nb, const int32_t* cu_q, const int32_t* ctx_start, int n_seq, int T, int H, int R,
                                int dr, int bs, float scale, int window /* 0: causal */, const void* gate /* or NULL */,

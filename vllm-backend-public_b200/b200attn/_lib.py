@@ -20,12 +20,12 @@ CORE_LIB_PATH = PKG_ROOT / "lib" / "libb200core.so"
 
 B2_OK, B2_EINVAL, B2_EUNSUPPORTED, B2_ECUDA, B2_ENOMEM, B2_ENOTFOUND, B2_EEXISTS = 0, -1, -2, -3, -4, -5, -6
 KV_BF16, KV_FP8_E4M3 = 0, 1
-ABI_VERSION = 4
+ABI_VERSION = 5
 ACT_BF16, ACT_F32 = 0, 1
 NORM_LAYER, NORM_RMS = 0, 1
 ROUTE_TOPK_SOFTMAX, ROUTE_SOFTMAX_ALL, ROUTE_SIGMOID_GROUPED = 0, 1, 2
 GLU_SILU, GLU_CLAMPED, GLU_GELU_TANH, FF_RELU_SQ = 0, 1, 2, 3
-DECAY_HEAD_SOFTPLUS, DECAY_CHANNEL_SOFTPLUS, DECAY_CHANNEL_SIGMOID_POW = 0, 1, 2
+DECAY_HEAD_SOFTPLUS, DECAY_CHANNEL_SOFTPLUS, DECAY_CHANNEL_SIGMOID_POW, DECAY_HEAD_CONST = 0, 1, 2, 3
 GATE_SILU, GATE_SIGMOID = 0, 1
 
 _ERRNAMES = {-1: "B2_EINVAL", -2: "B2_EUNSUPPORTED", -3: "B2_ECUDA", -4: "B2_ENOMEM",
@@ -121,6 +121,9 @@ SIGNATURES = {
     "b2_qknorm_cache": (i32, [vp, i64, i32, i32, i32, i32, i32, i32, vp, vp, f32, vp, i32, vp, vp, vp, vp]),
     "b2_chunk_attention": (i32, [vp, vp, vp, vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, i32, f32, i32, f32,
                                  f32, vp]),
+    "b2_masked_attention": (i32, [vp, vp, vp, vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, i32, f32, i32, i32, i32,
+                                  f32, f32, vp, vp, i64, vp]),
+    "b2_qk_rope_cache": (i32, [vp, i64, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, i32, vp, i32, vp, vp, vp, vp]),
     "b2_moe_tile_rows": (i32, []),
     "b2_moe_capacity": (i32, [i32, i32]),
     "b2_moe_route": (i32, [vp, i64, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp, vp]),
@@ -133,6 +136,7 @@ SIGNATURES = {
     "b2_moe_experts": (i32, [vp, i64, vp, vp, vp, i64, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, i64, i32, f32,
                              f32, vp]),
     "b2_sandwich_norm": (i32, [vp, i32, i32, vp, i64, vp, vp, vp, vp, f32, i32, vp, i64, i32, vp]),
+    "b2_row_norm": (i32, [vp, i64, vp, i64, i32, i32, i32, vp, f32, vp]),
     "b2_relu_sq": (i32, [vp, i64, vp, i64, i32, i32, i32, vp]),
     "b2_glu_and_mul": (i32, [vp, i64, vp, i64, i32, i32, i32, i32, f32, f32, vp]),
     "b2_gate_mul": (i32, [vp, i64, vp, i64, vp, i64, i32, i32, i32, i32, f32, vp]),
@@ -141,6 +145,8 @@ SIGNATURES = {
     "b2_shift_state": (i32, [vp, i32, vp, i32, f32, vp, vp, vp, i32, vp, vp]),
     "b2_softcap": (i32, [vp, i64, i32, i32, i32, f32, vp]),
     "b2_latent_prep": (i32, [vp, i64, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, f32, vp, vp, i32, vp, i32, vp, vp, vp]),
+    "b2_latent_prep_rows": (i32, [vp, i64, vp, i64, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, f32, vp, vp, i32, vp, i32, vp,
+                                  vp, vp]),
     "b2_latent_attention": (i32, [vp, vp, vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, f32, i32, vp, i64, vp, i64,
                                   vp]),
     "b2_latent_gather": (i32, [vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, vp]),

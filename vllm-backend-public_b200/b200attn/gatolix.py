@@ -359,15 +359,11 @@ class GatolixModel:
                 continue
             windows = [m.window for i, m in enumerate(specs) if i == o or m.kv_from == o]
             reach = 0 if 0 in windows else max(windows)
-            cu, lo = [0], []
-            for q, kv in zip(prefill.q_lens_host, prefill.kv_lens_host):
-                first = max(0, kv - q - (reach - 1)) if reach else 0
-                lo.append(first)
-                cu.append(cu[-1] + kv - first)
-            if cu[-1] > PROMPT_PER_HEAD_MAX_CONTEXT * prefill.total_tokens:
+            one = ops.latent_prompt_plan(prefill.q_lens_host, prefill.kv_lens_host, reach,
+                                         PROMPT_PER_HEAD_MAX_CONTEXT * prefill.total_tokens, self.dev)
+            if one is None:
                 return None
-            meta = torch.tensor(cu + lo, dtype=torch.int32).to(self.dev, non_blocking=True)
-            plan[o] = (cu[-1], meta[:len(cu)], meta[len(cu):])
+            plan[o] = one
         return plan
 
     def _mixer(self, li: int, h: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, batch: ops.SeqBatch,

@@ -643,7 +643,7 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor] = None, see
 from dataclasses import dataclass  # noqa: E402
 
 from ._lib import (ACT_BF16, ACT_F32, DECAY_CHANNEL_SIGMOID_POW, DECAY_CHANNEL_SOFTPLUS,  # noqa: E402,F401
-                   DECAY_HEAD_SOFTPLUS, FF_RELU_SQ, GATE_SIGMOID, GATE_SILU, GLU_CLAMPED, GLU_GELU_TANH, GLU_SILU, NORM_LAYER,
+                   DECAY_HEAD_CONST, DECAY_HEAD_SOFTPLUS, FF_RELU_SQ, GATE_SIGMOID, GATE_SILU, GLU_CLAMPED, GLU_GELU_TANH, GLU_SILU, NORM_LAYER,
                    NORM_RMS, ROUTE_SIGMOID_GROUPED, ROUTE_SOFTMAX_ALL, ROUTE_TOPK_SOFTMAX)
 
 
@@ -824,12 +824,15 @@ def qknorm_cache(qkv: torch.Tensor, H: int, G: int, dk: int, dv: int, q_w: Optio
 
 
 def chunk_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, batch: SeqBatch, scale: float,
-                    chunk: int = 0, sink: float = 0.0, sink_logit: float = 0.0) -> torch.Tensor:
+                    chunk: int = 0, sink: float = 0.0, sink_logit: float = 0.0, window: int = 0, keep_first: int = 0,
+                    sink_logits: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of q [T, H, dk] over the paged pools.  Row at position p sees positions j <= p with
-    j // chunk == p // chunk (chunk = 0: all j <= p); the denominator carries sink * exp(sink_logit).
-    Returns [T, H, dv] of q's dtype.  b2_chunk_attention."""
+    j // chunk == p // chunk (chunk = 0: all j <= p) and, with a window > 0, p - j < window or j < keep_first; the
+    denominator carries sink * exp(sink_logit), or sink * exp(sink_logits[h]) with one fp32 logit per query head; with
+    gate [T, H] (q's dtype, a column slice of a wider row is fine) head h's output is multiplied by sigmoid(gate[t, h]).
+    Returns [T, H, dv] of q's dtype.  b2_masked_attention."""
     lib = _lib.load()
-    dev = _need_cuda(q=q, k_cache=k_cache, v_cache=v_cache)
+    dev = _need_cuda(q=q, k_cache=k_cache, v_cache=v_cache, sink_logits=sink_logits, gate=gate)
     T, H, dk = q.shape
     nb, G, bs, dv = v_cache.shape
     if not q.is_contiguous() or k_cache.dtype != q.dtype or v_cache.dtype != q.dtype or tuple(k_cache.shape) != (nb, G, bs, dk):
@@ -838,11 +841,48 @@ def chunk_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     if bt is None or bt.dtype != torch.int32 or bt.dim() != 2 or bt.stride(1) != 1 or bt.shape[0] < batch.n_seq \
             or (bt.shape[0] > 1 and bt.stride(0) != bt.shape[1]):
         raise ValueError("block_tables must be a contiguous int32 [n_seq, max_nb]")
+    _f32(sink_logits, "sink_logits", (H,))
+    gs = 0
+    if gate is not None:
+        if gate.dtype != q.dtype or gate.dim() != 2 or tuple(gate.shape) != (T, H) or (H > 1 and gate.stride(1) != 1):
+            raise ValueError("gate must be [T, H] of q's dtype with a contiguous last axis")
+        gs = gate.stride(0) if T > 1 else H
     out = torch.empty(T, H, dv, dtype=q.dtype, device=dev)
-    _lib.check(lib.b2_chunk_attention(_ptr(out), _ptr(q), _ptr(k_cache), _ptr(v_cache), _act(q, "q"), _ptr(bt), bt.shape[1],
-                                      _ptr(batch.cu_q), _ptr(batch.ctx_start), batch.n_seq, T, H, G, dk, dv, bs,
-                                      float(scale), int(chunk), float(sink), float(sink_logit), _stream(dev)))
+    _lib.check(lib.b2_masked_attention(_ptr(out), _ptr(q), _ptr(k_cache), _ptr(v_cache), _act(q, "q"), _ptr(bt), bt.shape[1],
+                                       _ptr(batch.cu_q), _ptr(batch.ctx_start), batch.n_seq, T, H, G, dk, dv, bs,
+                                       float(scale), int(chunk), int(window), int(keep_first), float(sink), float(sink_logit),
+                                       _ptr(sink_logits), _ptr(gate), gs, _stream(dev)))
     return out
+
+
+def qk_rope_cache(qkv: torch.Tensor, H: int, G: int, dk: int, dv: int, positions: torch.Tensor, cos_sin: Optional[torch.Tensor],
+                  rot_dims: int, slots: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, interleaved: bool = False,
+                  v_from_k: bool = False) -> torch.Tensor:
+    """Rows qkv [T, >= H*dk + G*dk (+ G*dv)] = q | k (| v), biases already added: the first rot_dims entries of every q and k
+    head turn by the token's position (pairs (i, i + rot_dims/2), interleaved: (2i, 2i + 1); cos_sin from rotary_table),
+    rotated k goes to k_cache [nb, G, bs, dk] and v -- with v_from_k the k heads as projected, before the rotation -- to
+    v_cache [nb, G, bs, dv] at slots[t] (< 0 skips).  Returns the rotated q [T, H, dk].  b2_qk_rope_cache."""
+    lib = _lib.load()
+    dev = _need_cuda(qkv=qkv, slots=slots, k_cache=k_cache, v_cache=v_cache, positions=positions, cos_sin=cos_sin)
+    T, P, ps = _mat(qkv, "qkv")
+    if P < H * dk + G * dk + (0 if v_from_k else G * dv):
+        raise ValueError("qkv is narrower than its heads")
+    nb, bs = k_cache.shape[0], k_cache.shape[2]
+    if tuple(k_cache.shape) != (nb, G, bs, dk) or tuple(v_cache.shape) != (nb, G, bs, dv) or not k_cache.is_contiguous() \
+            or not v_cache.is_contiguous() or k_cache.dtype != qkv.dtype or v_cache.dtype != qkv.dtype:
+        raise ValueError("k_cache / v_cache must be contiguous [nb, G, bs, dk] / [nb, G, bs, dv] of qkv's dtype")
+    if slots.dtype != torch.int64 or slots.shape != (T,) or not slots.is_contiguous():
+        raise ValueError("slots must be contiguous int64 [T]")
+    if positions.dtype != torch.int32 or positions.shape != (T,) or not positions.is_contiguous():
+        raise ValueError("positions must be contiguous int32 [T]")
+    if rot_dims and (cos_sin is None or cos_sin.dtype != torch.float32 or cos_sin.dim() != 2 or cos_sin.shape[1] != rot_dims
+                     or not cos_sin.is_contiguous()):
+        raise ValueError(f"cos_sin must be contiguous fp32 [max_pos, {rot_dims}]")
+    q = torch.empty(T, H, dk, dtype=qkv.dtype, device=dev)
+    _lib.check(lib.b2_qk_rope_cache(_ptr(qkv), ps, _act(qkv, "qkv"), T, H, G, dk, dv, int(v_from_k), int(rot_dims),
+                                    int(interleaved), _ptr(positions), _ptr(cos_sin), cos_sin.shape[0] if rot_dims else 1,
+                                    _ptr(slots), bs, _ptr(q), _ptr(k_cache), _ptr(v_cache), _stream(dev)))
+    return q
 
 
 def moe_route(h: torch.Tensor, w_router: torch.Tensor, bias: Optional[torch.Tensor], top: int,
@@ -1037,7 +1077,8 @@ def recur_prep(proj: torch.Tensor, H: int, G: int, dk: int, dv: int, batch: SeqB
     optional SiLU, optional unit vectors for the q and k heads (x / sqrt(sum x^2 + unit_eps)), q times q_scale,
     beta = sigmoid(proj[:, off_beta + h]) when off_beta >= 0, and the decay: DECAY_HEAD_SOFTPLUS [T, H] from proj[:, off_a + h],
     A_log [H], decay_bias [H]; DECAY_CHANNEL_SOFTPLUS [T, H, dk] = exp(-exp(A_log[h]) softplus(a + decay_bias));
-    DECAY_CHANNEL_SIGMOID_POW [T, H, dk] = sigmoid(a + decay_bias)^(1 / tau), a fp32 [T, H*dk].  Everything after the
+    DECAY_CHANNEL_SIGMOID_POW [T, H, dk] = sigmoid(a + decay_bias)^(1 / tau), a fp32 [T, H*dk]; DECAY_HEAD_CONST [T, H] =
+    decay_bias [H], one fixed number per head.  Everything after the
     projection in fp32.  Returns fp32 qkv [T, C], beta [T, H] or None, decay.  b2_recur_prep."""
     lib = _lib.load()
     dev = _need_cuda(proj=proj, conv_w=conv_w, conv_state=conv_state, a=a, A_log=A_log, decay_bias=decay_bias)
@@ -1050,7 +1091,7 @@ def recur_prep(proj: torch.Tensor, H: int, G: int, dk: int, dv: int, batch: SeqB
     if taps > 1 and (conv_w is None or conv_state is None or conv_state.dtype != proj.dtype or not conv_state.is_contiguous()
                      or tuple(conv_state.shape[1:]) != (taps - 1, C)):
         raise ValueError(f"a convolution needs conv_w and a contiguous conv_state [slots, {taps - 1}, {C}] of proj's dtype")
-    per_channel = decay_mode != DECAY_HEAD_SOFTPLUS
+    per_channel = decay_mode not in (DECAY_HEAD_SOFTPLUS, DECAY_HEAD_CONST)
     a_stride = 0
     if per_channel:
         if a is None or a.dtype != torch.float32 or a.dim() != 2 or a.shape != (T, H * dk) or a.stride(1) != 1:
@@ -1058,8 +1099,10 @@ def recur_prep(proj: torch.Tensor, H: int, G: int, dk: int, dv: int, batch: SeqB
         a_stride = a.stride(0) if T > 1 else H * dk
         _f32(decay_bias, "decay_bias", (H * dk,))
     else:
-        if off_a < 0 or off_a + H > P:
+        if decay_mode == DECAY_HEAD_SOFTPLUS and (off_a < 0 or off_a + H > P):
             raise ValueError("off_a outside proj")
+        if decay_bias is None:
+            raise ValueError("a decay per head needs decay_bias [H]")
         _f32(decay_bias, "decay_bias", (H,))
     _f32(A_log, "A_log", (H,))
     if batch.state_slots is None:
@@ -1200,6 +1243,18 @@ def sandwich_norm(x: torch.Tensor, y: Optional[torch.Tensor] = None, post_w: Opt
     return h
 
 
+def row_norm(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float) -> torch.Tensor:
+    """x / sqrt(mean(x^2) + eps) * weight over activation rows [T, n] (a column slice of a wider row is fine; statistics in
+    fp32).  Returns a contiguous [T, n] of x's dtype.  b2_row_norm."""
+    lib = _lib.load()
+    dev = _need_cuda(x=x, weight=weight)
+    T, n, xs = _mat(x, "x")
+    _f32(weight, "weight", (n,))
+    out = torch.empty(T, n, dtype=x.dtype, device=dev)
+    _lib.check(lib.b2_row_norm(_ptr(out), n, _ptr(x), xs, _act(x, "x"), T, n, _ptr(weight), float(eps), _stream(dev)))
+    return out
+
+
 def relu_sq(x: torch.Tensor) -> torch.Tensor:
     """max(x, 0)^2 over rows [T, I].  b2_relu_sq."""
     lib = _lib.load()
@@ -1257,16 +1312,20 @@ def rotary_table(max_pos: int, dims: int, base: float, scaling: Optional[dict], 
 
 def latent_prep(proj: torch.Tensor, H: int, dn: int, dr: int, rot_dims: int, R: int, q_off: int, dkv_off: int,
                 norm_w: Optional[torch.Tensor], eps: float, positions: torch.Tensor, cos_sin: torch.Tensor,
-                slots: Optional[torch.Tensor], cache: Optional[torch.Tensor], qa: Optional[torch.Tensor] = None) -> torch.Tensor:
+                slots: Optional[torch.Tensor], cache: Optional[torch.Tensor], qa: Optional[torch.Tensor] = None,
+                kv: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Rows proj [T, ...] hold the query heads [dn | dr] from column q_off and, when dkv_off >= 0, the down-projection
-    [R | dr] from column dkv_off.  Writes the rotated dr part of every query head to qa[t, h, R:], and (dkv_off >= 0) the
+    [R | dr] from column dkv_off -- of proj, or of kv [T, ...] when the two come out of different products.  Writes the rotated dr part of every query head to qa[t, h, R:], and (dkv_off >= 0) the
     RMS-normed latent and the rotated shared key part to cache [nb, bs, R + dr] at slots[t] (< 0 skips).  Returns qa
     [T, H, R + dr] of proj's dtype, whose first R columns per head are left for the absorbed query.  b2_latent_prep."""
     lib = _lib.load()
     dev = _need_cuda(proj=proj, norm_w=norm_w, positions=positions, cos_sin=cos_sin, slots=slots, cache=cache, qa=qa)
     T, P, ps = _mat(proj, "proj")
-    if q_off + H * (dn + dr) > P or (dkv_off >= 0 and dkv_off + R + dr > P):
-        raise ValueError("proj is narrower than its column map")
+    kv = proj if kv is None else kv
+    Tk, Pk, ks = _mat(kv, "kv")
+    if q_off + H * (dn + dr) > P or (dkv_off >= 0 and dkv_off + R + dr > Pk) or Tk != T or kv.dtype != proj.dtype:
+        raise ValueError("proj / kv are narrower than their column map, or differ in rows or dtype")
+    _need_cuda(kv=kv)
     if positions.dtype != torch.int32 or positions.shape != (T,) or not positions.is_contiguous():
         raise ValueError("positions must be contiguous int32 [T]")
     if cos_sin.dtype != torch.float32 or cos_sin.dim() != 2 or cos_sin.shape[1] != rot_dims or not cos_sin.is_contiguous():
@@ -1283,9 +1342,9 @@ def latent_prep(proj: torch.Tensor, H: int, dn: int, dr: int, rot_dims: int, R: 
         qa = torch.empty(T, H, R + dr, dtype=proj.dtype, device=dev)
     elif tuple(qa.shape) != (T, H, R + dr) or qa.dtype != proj.dtype or not qa.is_contiguous():
         raise ValueError("qa must be contiguous [T, H, R + dr] of proj's dtype")
-    _lib.check(lib.b2_latent_prep(_ptr(proj), ps, _act(proj, "proj"), T, H, dn, dr, rot_dims, R, q_off, dkv_off, _ptr(norm_w),
-                                  float(eps), _ptr(positions), _ptr(cos_sin), cos_sin.shape[0], _ptr(slots), bs, _ptr(qa),
-                                  _ptr(cache) if dkv_off >= 0 else None, _stream(dev)))
+    _lib.check(lib.b2_latent_prep_rows(_ptr(proj), ps, _ptr(kv), ks, _act(proj, "proj"), T, H, dn, dr, rot_dims, R, q_off, dkv_off,
+                                       _ptr(norm_w), float(eps), _ptr(positions), _ptr(cos_sin), cos_sin.shape[0], _ptr(slots),
+                                       bs, _ptr(qa), _ptr(cache) if dkv_off >= 0 else None, _stream(dev)))
     return qa
 
 
@@ -1322,6 +1381,22 @@ def window_attention_ok(dtype: torch.dtype, dn: int, dr: int, dv: int) -> bool:
     """Shapes b2_window_attention takes."""
     return dtype == torch.bfloat16 and dn % 8 == 0 and dr % 8 == 0 and (dn + dr) % 16 == 0 and dn + dr > 0 and dv % 16 == 0 \
         and 0 < dv <= 128
+
+
+def latent_prompt_plan(q_lens, kv_lens, reach: int, max_rows: int, device):
+    """Host-side plan of the pool rows that a step's prompt portions can see, for latent_gather / window_attention: portion
+    i has q_lens[i] rows and kv_lens[i] tokens in the pool once they are written (host integers); with reach > 0 (the widest
+    window) its rows start at the first row's window, else at position 0.  Returns (N, cu_k, k_lo) -- the row count and the
+    two int32 device tensors --, or None when more than max_rows rows would have to be gathered."""
+    cu, lo = [0], []
+    for q, kv in zip(q_lens, kv_lens):
+        first = max(0, kv - q - (reach - 1)) if reach else 0
+        lo.append(first)
+        cu.append(cu[-1] + kv - first)
+    if cu[-1] > max_rows:
+        return None
+    meta = torch.tensor(cu + lo, dtype=torch.int32).to(device, non_blocking=True)
+    return cu[-1], meta[:len(cu)], meta[len(cu):]
 
 
 def latent_gather(cache: torch.Tensor, block_tables: torch.Tensor, cu_k: torch.Tensor, k_lo: torch.Tensor, n_seq: int,

@@ -4,7 +4,11 @@
 //   * a block-local causal mask: position i sees j <= i with floor(j / chunk) == floor(i / chunk), blocks counted from
 //     position 0 of the sequence (chunk = 0: plain causal),
 //   * a sink: `sink` is added to the softmax denominator as exp(sink_logit - max), a key with no value (sink = 0: none;
-//     sink = 1 with logit 0 gives p_j = exp(s_j) / (1 + sum exp(s))).
+//     sink = 1 with logit 0 gives p_j = exp(s_j) / (1 + sum exp(s))); the logit may also be one learned number per
+//     query head (sink_logits [H], not scaled),
+//   * a sliding window that keeps the first tokens: position i sees j <= i with i - j < window or j < keep_first
+//     (window = 0: no window).  A query then reads the kept keys and its window's keys and nothing between them,
+//   * a sigmoid gate per (token, head) on the head's output.
 // Key size dk and value size dv are independent; K and V live in separate paged pools
 //   k_cache [num_blocks, G, bs, dk],  v_cache [num_blocks, G, bs, dv]      (activation type).
 //
@@ -13,6 +17,10 @@
 //   b2_qk_prep_cache     the same pass with the norm optional and a query temperature: the query of the token at position p
 //                        is multiplied by 1 + coef * ln(floor((p + 1) / every) + 1) (fp32), so queries sharpen as the
 //                        context grows in steps of `every` positions (coef = 0: none).
+//   b2_qk_rope_cache     rows [q | k] or [q | k | v]: the first rot_dims entries of every q and k head are rotated by the
+//                        token's position (pairs (i, i + rot_dims/2) or (2i, 2i + 1); fp32 table [max_pos, rot_dims] =
+//                        cos | sin halves), q to q_out, rotated k to the K pool; the V pool receives v, or, for designs
+//                        whose values ARE the keys, the k heads as projected (before the rotation).
 //   b2_chunk_attention   per (token, head) one warp: scores of 32 keys at a time (a lane per key), online softmax in fp32
 //                        seeded with the sink, P.V with a lane per value column.  With the mask a query touches at most
 //                        `chunk` keys wherever it stands, so prompt chunks and decode rows run the same kernel; a decode
@@ -24,6 +32,122 @@
 namespace {
 
 constexpr int kMaxDvPerLane = 16;                    // dv <= 512
+
+// The keys a query at position `pos` may see, as one compact index range [0, n): first the kept keys lo .. lo+nfirst-1
+// (the sequence's first tokens that lie before the window), then wlo .. pos.  Without a window nfirst = 0 and wlo = lo.
+struct KeySpan {
+    int lo, nfirst, wlo, n;
+    __device__ __forceinline__ int key(int c) const { return c < nfirst ? lo + c : wlo + (c - nfirst); }
+};
+__device__ __forceinline__ KeySpan key_span(int pos, int last, int chunk, int window, int keep_first) {
+    KeySpan s;
+    s.lo = chunk > 0 ? (pos / chunk) * chunk : 0;
+    s.wlo = window > 0 ? max(s.lo, pos - window + 1) : s.lo;
+    s.nfirst = (window > 0 && keep_first > s.lo) ? max(0, min(keep_first, s.wlo) - s.lo) : 0;
+    s.n = s.nfirst + (last - s.wlo + 1);
+    return s;
+}
+// what the masks leave of key j for the query at position i
+__device__ __forceinline__ bool key_visible(int i, int j, int lo_i, int window, int keep_first) {
+    return j <= i && j >= lo_i && (window <= 0 || i - j < window || j < keep_first);
+}
+
+// Rows [q | k] (+ [v]): partial rotation of the q and k heads, K (rotated) and V pool writes; see the file comment.
+template <typename T>
+__global__ void qk_rope_cache_kernel(const T* __restrict__ qkv, int64_t qkv_stride, int H, int G, int dk, int dv, bool v_from_k,
+                                     int rot_dims, bool interleaved, const int32_t* __restrict__ positions,
+                                     const float* __restrict__ cos_sin, int max_pos, const int64_t* __restrict__ slots, int bs,
+                                     T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache) {
+    const int row = blockIdx.x;
+    const T* src = qkv + (size_t)row * qkv_stride;
+    int pos = positions[row];
+    pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+    const float* cs = cos_sin + (size_t)pos * rot_dims;
+    const int half = rot_dims / 2;
+    const int64_t slot = slots[row];
+    const int64_t blk = slot >= 0 ? slot / bs : 0;
+    const int off = slot >= 0 ? (int)(slot % bs) : 0;
+    // q and k heads: element i of a head
+    for (int idx = threadIdx.x; idx < (H + G) * dk; idx += blockDim.x) {
+        const int hd = idx / dk, i = idx % dk;
+        if (hd >= H && slot < 0) continue;
+        const T* v = src + (size_t)hd * dk;
+        float x = b2::ld(v + i);
+        if (i < rot_dims) {
+            int pr, partner;
+            bool second;
+            if (interleaved) { pr = i >> 1; partner = i ^ 1; second = i & 1; }
+            else { second = i >= half; pr = second ? i - half : i; partner = second ? i - half : i + half; }
+            const float c = cs[pr], sn = cs[half + pr], other = b2::ld(v + partner);
+            x = second ? fmaf(x, c, other * sn) : fmaf(x, c, -other * sn);
+        }
+        T* dst = hd < H ? q_out + ((size_t)row * H + hd) * dk : k_cache + (((size_t)blk * G + (hd - H)) * bs + off) * dk;
+        b2::st(dst + i, x);
+    }
+    if (slot < 0) return;
+    const T* vsrc = v_from_k ? src + (size_t)H * dk : src + (size_t)(H + G) * dk;
+    for (int idx = threadIdx.x; idx < G * dv; idx += blockDim.x) {
+        const int g = idx / dv, i = idx % dv;
+        v_cache[(((size_t)blk * G + g) * bs + off) * dv + i] = vsrc[idx];
+    }
+}
+
+// The same with four entries per access (8 or 16 bytes): every size a multiple of four, the rotated entries a multiple of
+// eight in the (i, i + rot_dims/2) layout so that a group of four and its partners never straddle the halves.
+template <typename T>
+__global__ void __launch_bounds__(256)
+qk_rope_cache_vec_kernel(const T* __restrict__ qkv, int64_t qkv_stride, int H, int G, int dk, int dv, bool v_from_k, int rot_dims,
+                         bool interleaved, const int32_t* __restrict__ positions, const float* __restrict__ cos_sin, int max_pos,
+                         const int64_t* __restrict__ slots, int bs, T* __restrict__ q_out, T* __restrict__ k_cache,
+                         T* __restrict__ v_cache) {
+    const int row = blockIdx.x;
+    const T* src = qkv + (size_t)row * qkv_stride;
+    int pos = positions[row];
+    pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+    const float* cs = cos_sin + (size_t)pos * rot_dims;
+    const int half = rot_dims / 2;
+    const int64_t slot = slots[row];
+    const int64_t blk = slot >= 0 ? slot / bs : 0;
+    const int off = slot >= 0 ? (int)(slot % bs) : 0;
+    const int per = dk / 4, nqk = (slot >= 0 ? H + G : H) * per;
+    for (int idx = threadIdx.x; idx < nqk; idx += blockDim.x) {
+        const int hd = idx / per, i = (idx % per) * 4;
+        const T* v = src + (size_t)hd * dk;
+        float x[4];
+        b2::ld4(v + i, x);
+        if (i < rot_dims) {
+            if (interleaved) {
+#pragma unroll
+                for (int c = 0; c < 4; c += 2) {
+                    const float co = cs[(i + c) >> 1], si = cs[half + ((i + c) >> 1)], a = x[c], b = x[c + 1];
+                    x[c] = fmaf(a, co, -b * si);
+                    x[c + 1] = fmaf(b, co, a * si);
+                }
+            } else {
+                const bool second = i >= half;
+                const int pr = second ? i - half : i;
+                float y[4];
+                b2::ld4(v + (second ? i - half : i + half), y);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const float co = cs[pr + c], si = cs[half + pr + c];
+                    x[c] = second ? fmaf(x[c], co, y[c] * si) : fmaf(x[c], co, -y[c] * si);
+                }
+            }
+        }
+        T* dst = hd < H ? q_out + ((size_t)row * H + hd) * dk : k_cache + (((size_t)blk * G + (hd - H)) * bs + off) * dk;
+        b2::st4(dst + i, x);
+    }
+    if (slot < 0) return;
+    const T* vsrc = v_from_k ? src + (size_t)H * dk : src + (size_t)(H + G) * dk;
+    const int pv = dv / 4;
+    for (int idx = threadIdx.x; idx < G * pv; idx += blockDim.x) {
+        const int g = idx / pv, i = (idx % pv) * 4;
+        float x[4];
+        b2::ld4(vsrc + (size_t)g * dv + i, x);
+        b2::st4(v_cache + (((size_t)blk * G + g) * bs + off) * dv + i, x);
+    }
+}
 
 template <typename T>
 __global__ void qknorm_cache_kernel(const T* __restrict__ qkv, int64_t qkv_stride, int H, int G, int dk, int dv,
@@ -76,8 +200,10 @@ template <typename T>
 __global__ void chunk_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                                        const int32_t* __restrict__ block_tables, int max_nb,
                                        const int32_t* __restrict__ cu_q, const int32_t* __restrict__ ctx_start, int n_seq,
-                                       int rows, int H, int G, int dk, int dv, int bs, float scale, int chunk, float sink,
-                                       float sink_logit, int skip_rows_from, T* __restrict__ out) {
+                                       int rows, int H, int G, int dk, int dv, int bs, float scale, int chunk, int window,
+                                       int keep_first, float sink, float sink_logit, const float* __restrict__ sink_logits,
+                                       const T* __restrict__ gate, int64_t gate_stride, int skip_rows_from,
+                                       T* __restrict__ out) {
     extern __shared__ float q_sm[];                  // [warps, dk]
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int item = blockIdx.x * (blockDim.x >> 5) + wid;       // (row, head)
@@ -92,22 +218,23 @@ __global__ void chunk_attention_kernel(const T* __restrict__ q, const T* __restr
         return;
     }
     const int pos = ctx + row - cu_q[seq];
-    const int lo = chunk > 0 ? (pos / chunk) * chunk : 0;
+    const KeySpan span = key_span(pos, pos, chunk, window, keep_first);
     const int g = hh / (H / G);
     float* qs = q_sm + (size_t)wid * dk;
     const T* qv = q + (size_t)item * dk;
     for (int i = lane; i < dk; i += 32) qs[i] = b2::ld(qv + i) * scale;
     __syncwarp();
     const int32_t* bt = block_tables + (size_t)seq * max_nb;
-    float m = sink > 0.f ? sink_logit : -INFINITY, l = sink;      // the sink seeds the running maximum and denominator
+    float m = sink > 0.f ? (sink_logits ? sink_logits[hh] : sink_logit) : -INFINITY, l = sink;      // the sink seeds the running maximum and denominator
     float acc[kMaxDvPerLane];
 #pragma unroll
     for (int c = 0; c < kMaxDvPerLane; ++c) acc[c] = 0.f;
-    for (int j0 = lo; j0 <= pos; j0 += 32) {
-        const int j = j0 + lane;
+    for (int c0 = 0; c0 < span.n; c0 += 32) {
+        const bool in = c0 + lane < span.n;
+        const int j = span.key(c0 + lane);
         float s = -INFINITY;
         size_t vbase = 0;
-        if (j <= pos) {
+        if (in) {
             const size_t tile = ((size_t)bt[j / bs] * G + g) * bs + (j % bs);
             const T* kr = k_cache + tile * dk;
             vbase = tile * dv;
@@ -117,12 +244,12 @@ __global__ void chunk_attention_kernel(const T* __restrict__ q, const T* __restr
         }
         const float m_new = fmaxf(m, b2::warp_max(s));
         const float corr = m == -INFINITY ? 0.f : __expf(m - m_new);
-        const float p = j <= pos ? __expf(s - m_new) : 0.f;
+        const float p = in ? __expf(s - m_new) : 0.f;
         l = l * corr + b2::warp_sum(p);
         m = m_new;
 #pragma unroll
         for (int c = 0; c < kMaxDvPerLane; ++c) acc[c] *= corr;
-        const int nk = min(32, pos - j0 + 1);
+        const int nk = min(32, span.n - c0);
         for (int kk = 0; kk < nk; ++kk) {
             const float pk = __shfl_sync(0xffffffffu, p, kk);
             const size_t vb = __shfl_sync(0xffffffffu, (unsigned long long)vbase, kk);
@@ -134,7 +261,8 @@ __global__ void chunk_attention_kernel(const T* __restrict__ q, const T* __restr
             }
         }
     }
-    const float inv = l > 0.f ? 1.f / l : 0.f;
+    float inv = l > 0.f ? 1.f / l : 0.f;
+    if (gate) inv *= b2::sigmoid_f(b2::ld(gate + (size_t)row * gate_stride + hh));
 #pragma unroll
     for (int c = 0; c < kMaxDvPerLane; ++c) {
         const int i = lane + 32 * c;
@@ -158,8 +286,9 @@ __global__ void __launch_bounds__(128)
 chunk_attention_group_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
                              const __nv_bfloat16* __restrict__ v_cache, const int32_t* __restrict__ block_tables, int max_nb,
                              const int32_t* __restrict__ cu_q, const int32_t* __restrict__ ctx_start, int n_seq, int H, int G,
-                             int dk, int dv, int bs, float scale, int chunk, float sink, float sink_logit, int skip_rows_from,
-                             __nv_bfloat16* __restrict__ out) {
+                             int dk, int dv, int bs, float scale, int chunk, int window, int keep_first, float sink,
+                             float sink_logit, const float* __restrict__ sink_logits, const __nv_bfloat16* __restrict__ gate,
+                             int64_t gate_stride, int skip_rows_from, __nv_bfloat16* __restrict__ out) {
     // q [QH][dk] | per warp: m [QH], l [QH], acc [QH][dv] | per warp: K tile [32][dk + 8], V tile [32][dv] (bf16)
     extern __shared__ __align__(16) float grp_sm[];
     const int row = blockIdx.x, g = blockIdx.y;
@@ -173,7 +302,7 @@ chunk_attention_group_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
         return;
     }
     const int pos = ctx + row - cu_q[seq];
-    const int lo = chunk > 0 ? (pos / chunk) * chunk : 0;
+    const KeySpan span = key_span(pos, pos, chunk, window, keep_first);
     const int32_t* bt = block_tables + (size_t)seq * max_nb;
     const int npairs = dv / 2;
     for (int h0 = 0; h0 < QHall; h0 += kGroupMaxHeads) {
@@ -190,26 +319,25 @@ chunk_attention_group_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
         float m[kGroupMaxHeads], l[kGroupMaxHeads], acc[kGroupMaxHeads][kGroupMaxPairs][2];
 #pragma unroll
         for (int h = 0; h < kGroupMaxHeads; ++h) {
-            m[h] = (w == 0 && sink > 0.f) ? sink_logit : -INFINITY;
+            m[h] = (w == 0 && sink > 0.f) ? (sink_logits ? sink_logits[g * QHall + h0 + min(h, QH - 1)] : sink_logit) : -INFINITY;
             l[h] = w == 0 ? sink : 0.f;
 #pragma unroll
             for (int c = 0; c < kGroupMaxPairs; ++c) acc[h][c][0] = acc[h][c][1] = 0.f;
         }
-        for (int j0 = lo + w * 32; j0 <= pos; j0 += 128) {
-            const int j = j0 + lane;
-            const bool valid = j <= pos;
+        for (int c0 = w * 32; c0 < span.n; c0 += 128) {
+            const bool valid = c0 + lane < span.n;
             float sc[kGroupMaxHeads];
 #pragma unroll
             for (int h = 0; h < kGroupMaxHeads; ++h) sc[h] = 0.f;
             // the warp's 32 keys: K and V rows gathered from the pages with every 16-byte copy in flight at once
-            const int nk = min(32, pos - j0 + 1);
+            const int nk = min(32, span.n - c0);
             __syncwarp();                                  // the previous tile has been read
             for (int idx = lane; idx < nk * (dk / 8); idx += 32) {
-                const int key = idx / (dk / 8), c = (idx % (dk / 8)) * 8, jk = j0 + key;
+                const int key = idx / (dk / 8), c = (idx % (dk / 8)) * 8, jk = span.key(c0 + key);
                 cp_async16(kt + key * ldk + c, k_cache + (((size_t)bt[jk / bs] * G + g) * bs + jk % bs) * dk + c);
             }
             for (int idx = lane; idx < nk * (dv / 8); idx += 32) {
-                const int key = idx / (dv / 8), c = (idx % (dv / 8)) * 8, jk = j0 + key;
+                const int key = idx / (dv / 8), c = (idx % (dv / 8)) * 8, jk = span.key(c0 + key);
                 cp_async16(vt + key * dv + c, v_cache + (((size_t)bt[jk / bs] * G + g) * bs + jk % bs) * dv + c);
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
@@ -315,7 +443,9 @@ chunk_attention_group_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
                     O = fmaf(px[2 + col], f, O);
                 }
             }
-            out[((size_t)row * H + (size_t)g * QHall + h0 + h) * dv + col] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+            float res = L > 0.f ? O / L : 0.f;
+            if (gate) res *= b2::sigmoid_f(__bfloat162float(gate[(size_t)row * gate_stride + (size_t)g * QHall + h0 + h]));
+            out[((size_t)row * H + (size_t)g * QHall + h0 + h) * dv + col] = __float2bfloat16_rn(res);
         }
     }
 }
@@ -334,8 +464,9 @@ __global__ void __launch_bounds__(128)
 chunk_attention_tile_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
                             const __nv_bfloat16* __restrict__ v_cache, const int32_t* __restrict__ block_tables, int max_nb,
                             const int32_t* __restrict__ cu_q, const int32_t* __restrict__ ctx_start, int n_seq, int H, int G,
-                            int bs, float scale_log2, int chunk, float sink, float sink_logit_log2,
-                            __nv_bfloat16* __restrict__ out) {
+                            int bs, float scale_log2, int chunk, int window, int keep_first, float sink,
+                            float sink_logit_log2, const float* __restrict__ sink_logits,
+                            const __nv_bfloat16* __restrict__ gate, int64_t gate_stride, __nv_bfloat16* __restrict__ out) {
     constexpr int DK = 16 * DKT, DV = 16 * DVT, LDK = DK + 8, LDV = DV + 8;
     extern __shared__ __align__(16) unsigned char tile_smem[];
     __nv_bfloat16* q_sm = reinterpret_cast<__nv_bfloat16*>(tile_smem);      // [64][LDK]
@@ -362,7 +493,8 @@ chunk_attention_tile_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
     const int r0 = cu_q[seq] + t0;
     const int rows = min(kTQ, cu_q[seq + 1] - r0);
     const int p0 = ctx_start[seq] + t0, p_last = p0 + rows - 1;
-    const int klo = chunk > 0 ? (p0 / chunk) * chunk : 0;
+    // the union of what the tile's rows see, as one compact range: kept first keys, then the first row's window .. p_last
+    const KeySpan span = key_span(p0, p_last, chunk, window, keep_first);
     const int32_t* bt = block_tables + (size_t)seq * max_nb;
 
     for (int idx = tid; idx < kTQ * (DK / 8); idx += 128) {
@@ -375,7 +507,9 @@ chunk_attention_tile_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
     const int i0 = p0 + w * 16 + gq, i1 = i0 + 8;                           // positions of this thread's two rows
     const int lo0 = chunk > 0 ? (i0 / chunk) * chunk : 0, lo1 = chunk > 0 ? (i1 / chunk) * chunk : 0;
     const int w_first = p0 + w * 16, w_last = w_first + 15;
-    const int w_lo = chunk > 0 ? (w_first / chunk) * chunk : 0;
+    const int w_clo = chunk > 0 ? (w_first / chunk) * chunk : 0;
+    const int w_lo = window > 0 ? max(w_clo, w_first - window + 1) : w_clo;   // the lowest key of the warp's rows' windows
+    if (sink_logits) sink_logit_log2 = sink_logits[hh] * 1.4426950408889634f;
     float m0 = sink > 0.f ? sink_logit_log2 : -INFINITY, m1 = m0;
     float l0 = tq == 0 ? sink : 0.f, l1 = l0;                               // partial sums per lane; the sink counted once
     float o[2 * DVT][4];
@@ -383,22 +517,25 @@ chunk_attention_tile_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
     for (int n = 0; n < 2 * DVT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
     const uint32_t q_base = b2::smem_u32(q_sm), k_base = b2::smem_u32(k_sm), v_base = b2::smem_u32(v_sm);
 
-    for (int kv0 = klo; kv0 <= p_last; kv0 += kTK) {
+    for (int kv0 = 0; kv0 < span.n; kv0 += kTK) {                           // kv0: compact key index of the tile's first key
         __syncthreads();                                                    // the previous tile is consumed (and Q is stored)
         for (int idx = tid; idx < kTK * (DK / 8); idx += 128) {
-            const int key = idx / (DK / 8), c = (idx % (DK / 8)) * 8, j = kv0 + key;
+            const int key = idx / (DK / 8), c = (idx % (DK / 8)) * 8, j = span.key(kv0 + key);
             uint4 v = make_uint4(0, 0, 0, 0);
             if (j <= p_last) v = *reinterpret_cast<const uint4*>(k_cache + (((size_t)bt[j / bs] * G + g) * bs + j % bs) * DK + c);
             *reinterpret_cast<uint4*>(k_sm + key * LDK + c) = v;
         }
         for (int idx = tid; idx < kTK * (DV / 8); idx += 128) {
-            const int key = idx / (DV / 8), c = (idx % (DV / 8)) * 8, j = kv0 + key;
+            const int key = idx / (DV / 8), c = (idx % (DV / 8)) * 8, j = span.key(kv0 + key);
             uint4 v = make_uint4(0, 0, 0, 0);
             if (j <= p_last) v = *reinterpret_cast<const uint4*>(v_cache + (((size_t)bt[j / bs] * G + g) * bs + j % bs) * DV + c);
             *reinterpret_cast<uint4*>(v_sm + key * LDV + c) = v;
         }
         __syncthreads();
-        if (kv0 > w_last || kv0 + kTK - 1 < w_lo) continue;                 // nothing in this tile is visible to the warp's rows
+        {   // nothing in this tile is visible to the warp's rows: all keys after them, or all before their windows and not kept
+            const int j_min = span.key(kv0), j_max = span.key(min(kv0 + kTK, span.n) - 1);
+            if (j_min > w_last || (j_max < w_lo && (window <= 0 || j_min >= keep_first))) continue;
+        }
         float sc[8][4];
 #pragma unroll
         for (int n = 0; n < 8; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
@@ -420,8 +557,8 @@ chunk_attention_tile_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
         for (int n = 0; n < 8; ++n) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const int j = kv0 + n * 8 + 2 * tq + (e & 1);
-                const bool ok = e < 2 ? (j >= lo0 && j <= i0) : (j >= lo1 && j <= i1);
+                const int j = span.key(kv0 + n * 8 + 2 * tq + (e & 1));
+                const bool ok = e < 2 ? key_visible(i0, j, lo0, window, keep_first) : key_visible(i1, j, lo1, window, keep_first);
                 sc[n][e] = ok ? sc[n][e] * scale_log2 : -INFINITY;
             }
             mx0 = fmaxf(mx0, fmaxf(sc[n][0], sc[n][1]));
@@ -474,8 +611,12 @@ chunk_attention_tile_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-    const float inv0 = l0 > 0.f ? 1.f / l0 : 0.f, inv1 = l1 > 0.f ? 1.f / l1 : 0.f;
+    float inv0 = l0 > 0.f ? 1.f / l0 : 0.f, inv1 = l1 > 0.f ? 1.f / l1 : 0.f;
     const int ra = w * 16 + gq, rb = ra + 8;
+    if (gate) {
+        if (ra < rows) inv0 *= b2::sigmoid_f(__bfloat162float(gate[(size_t)(r0 + ra) * gate_stride + hh]));
+        if (rb < rows) inv1 *= b2::sigmoid_f(__bfloat162float(gate[(size_t)(r0 + rb) * gate_stride + hh]));
+    }
 #pragma unroll
     for (int n = 0; n < 2 * DVT; ++n) {
         const int col = n * 8 + 2 * tq;
@@ -489,7 +630,8 @@ chunk_attention_tile_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
 template <int DKT, int DVT>
 int launch_tile(const void* q, const void* k_cache, const void* v_cache, const int32_t* block_tables, int max_nb,
                 const int32_t* cu_q, const int32_t* ctx_start, int n_seq, int T, int H, int G, int bs, float scale, int chunk,
-                float sink, float sink_logit, void* out, cudaStream_t st) {
+                int window, int keep_first, float sink, float sink_logit, const float* sink_logits, const void* gate,
+                int64_t gate_stride, void* out, cudaStream_t st) {
     constexpr int DK = 16 * DKT, DV = 16 * DVT;
     const size_t smem = (size_t)(kTQ * (DK + 8) + kTK * (DK + 8) + kTK * (DV + 8)) * sizeof(__nv_bfloat16);
     auto kern = chunk_attention_tile_kernel<DKT, DVT>;
@@ -497,8 +639,9 @@ int launch_tile(const void* q, const void* k_cache, const void* v_cache, const i
     const int tiles = (T + kTQ - 1) / kTQ + n_seq;          // upper bound on sum(ceil(len / 64)); spare CTAs leave at once
     kern<<<dim3(tiles, H), 128, smem, st>>>(static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_cache),
                                            static_cast<const __nv_bfloat16*>(v_cache), block_tables, max_nb, cu_q, ctx_start,
-                                           n_seq, H, G, bs, scale * 1.4426950408889634f, chunk, sink,
-                                           sink_logit * 1.4426950408889634f, static_cast<__nv_bfloat16*>(out));
+                                           n_seq, H, G, bs, scale * 1.4426950408889634f, chunk, window, keep_first, sink,
+                                           sink_logit * 1.4426950408889634f, sink_logits,
+                                           static_cast<const __nv_bfloat16*>(gate), gate_stride, static_cast<__nv_bfloat16*>(out));
     B2_CUDA_OK(cudaGetLastError());
     return B2_OK;
 }
@@ -538,12 +681,55 @@ extern "C" int b2_qk_prep_cache(const void* qkv, int64_t qkv_stride, int act_dty
     return B2_OK;
 }
 
+extern "C" int b2_qk_rope_cache(const void* qkv, int64_t qkv_stride, int act_dtype, int T, int H, int G, int dk, int dv,
+                                int v_from_k, int rot_dims, int interleaved, const int32_t* positions, const float* cos_sin,
+                                int max_pos, const int64_t* slots, int bs, void* q_out, void* k_cache, void* v_cache,
+                                void* stream) {
+    B2_REQUIRE(T >= 0 && H > 0 && G > 0 && H % G == 0 && dk > 0 && dv > 0 && bs > 0, B2_EINVAL, "qk_rope_cache: bad sizes");
+    B2_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= dk, B2_EINVAL,
+               "qk_rope_cache: %d rotated entries in heads of %d", rot_dims, dk);
+    B2_REQUIRE(!v_from_k || dv == dk, B2_EINVAL, "qk_rope_cache: values taken from the keys need dv == dk");
+    B2_REQUIRE(rot_dims == 0 || max_pos > 0, B2_EINVAL, "qk_rope_cache: empty rotation table");
+    if (T == 0) return B2_OK;
+    B2_REQUIRE(qkv && slots && q_out && k_cache && v_cache && positions && (cos_sin || rot_dims == 0), B2_EINVAL,
+               "qk_rope_cache: null pointer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t esz = act_dtype == B2_ACT_BF16 ? 2 : 4;
+    auto al = [&](const void* p) { return reinterpret_cast<uintptr_t>(p) % (4 * esz) == 0; };
+    const bool vec = dk % 4 == 0 && dv % 4 == 0 && qkv_stride % 4 == 0 && rot_dims % (interleaved ? 4 : 8) == 0 && al(qkv) && al(q_out) &&
+                     al(k_cache) && al(v_cache);
+    const int work = (H + G) * dk / (vec ? 4 : 1);
+    const int threads = work >= 256 ? 256 : (work >= 128 ? 128 : 64);
+    B2_DISPATCH_ACT(act_dtype, A, {
+        if (vec)
+            qk_rope_cache_vec_kernel<A><<<T, threads, 0, st>>>(
+                static_cast<const A*>(qkv), qkv_stride, H, G, dk, dv, v_from_k != 0, rot_dims, interleaved != 0, positions, cos_sin,
+                max_pos > 0 ? max_pos : 1, slots, bs, static_cast<A*>(q_out), static_cast<A*>(k_cache), static_cast<A*>(v_cache));
+        else
+            qk_rope_cache_kernel<A><<<T, threads, 0, st>>>(
+                static_cast<const A*>(qkv), qkv_stride, H, G, dk, dv, v_from_k != 0, rot_dims, interleaved != 0, positions, cos_sin,
+                max_pos > 0 ? max_pos : 1, slots, bs, static_cast<A*>(q_out), static_cast<A*>(k_cache), static_cast<A*>(v_cache));
+    });
+    B2_CUDA_OK(cudaGetLastError());
+    return B2_OK;
+}
+
 extern "C" int b2_chunk_attention(void* out, const void* q, const void* k_cache, const void* v_cache, int act_dtype,
                                   const int32_t* block_tables, int max_nb, const int32_t* cu_q, const int32_t* ctx_start,
                                   int n_seq, int T, int H, int G, int dk, int dv, int bs, float scale, int chunk, float sink,
                                   float sink_logit, void* stream) {
-    B2_REQUIRE(T >= 0 && H > 0 && G > 0 && H % G == 0 && dk > 0 && dv > 0 && bs > 0 && chunk >= 0 && sink >= 0.f, B2_EINVAL,
-               "chunk_attention: bad sizes");
+    return b2_masked_attention(out, q, k_cache, v_cache, act_dtype, block_tables, max_nb, cu_q, ctx_start, n_seq, T, H, G, dk, dv,
+                               bs, scale, chunk, 0, 0, sink, sink_logit, nullptr, nullptr, 0, stream);
+}
+
+extern "C" int b2_masked_attention(void* out, const void* q, const void* k_cache, const void* v_cache, int act_dtype,
+                                   const int32_t* block_tables, int max_nb, const int32_t* cu_q, const int32_t* ctx_start,
+                                   int n_seq, int T, int H, int G, int dk, int dv, int bs, float scale, int chunk, int window,
+                                   int keep_first, float sink, float sink_logit, const float* sink_logits, const void* gate,
+                                   int64_t gate_stride, void* stream) {
+    B2_REQUIRE(T >= 0 && H > 0 && G > 0 && H % G == 0 && dk > 0 && dv > 0 && bs > 0 && chunk >= 0 && sink >= 0.f && window >= 0 &&
+               keep_first >= 0, B2_EINVAL, "masked_attention: bad sizes");
+    B2_REQUIRE(!gate || gate_stride >= H, B2_EINVAL, "masked_attention: gate rows shorter than the heads");
     B2_REQUIRE(dv <= 32 * kMaxDvPerLane, B2_EUNSUPPORTED, "chunk_attention: value size %d above %d", dv, 32 * kMaxDvPerLane);
     if (T == 0 || n_seq == 0) return B2_OK;
     B2_REQUIRE(out && q && k_cache && v_cache && block_tables && cu_q && ctx_start, B2_EINVAL, "chunk_attention: null pointer");
@@ -562,7 +748,7 @@ extern "C" int b2_chunk_attention(void* out, const void* q, const void* k_cache,
 #define B2_TILE(a, b)                                                                                                     \
     if (dk == 16 * a && dv == 16 * b)                                                                                     \
         rc = launch_tile<a, b>(q, k_cache, v_cache, block_tables, max_nb, cu_q, ctx_start, n_seq, T, H, G, bs, scale, chunk, \
-                               sink, sink_logit, out, st);
+                               window, keep_first, sink, sink_logit, sink_logits, gate, gate_stride, out, st);
         B2_TILE(2, 2) B2_TILE(2, 4) B2_TILE(2, 6) B2_TILE(2, 8) B2_TILE(4, 2) B2_TILE(4, 4) B2_TILE(4, 6) B2_TILE(4, 8)
         B2_TILE(6, 2) B2_TILE(6, 4) B2_TILE(6, 6) B2_TILE(6, 8) B2_TILE(8, 2) B2_TILE(8, 4) B2_TILE(8, 6) B2_TILE(8, 8)
 #undef B2_TILE
@@ -577,7 +763,8 @@ extern "C" int b2_chunk_attention(void* out, const void* q, const void* k_cache,
             if (gsm > 48 * 1024) B2_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gsm));
             kern<<<dim3(T, G), 128, gsm, st>>>(static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_cache),
                                                static_cast<const __nv_bfloat16*>(v_cache), block_tables, max_nb, cu_q, ctx_start,
-                                               n_seq, H, G, dk, dv, bs, scale, chunk, sink, sink_logit, skip_from,
+                                               n_seq, H, G, dk, dv, bs, scale, chunk, window, keep_first, sink, sink_logit,
+                                               sink_logits, static_cast<const __nv_bfloat16*>(gate), gate_stride, skip_from,
                                                static_cast<__nv_bfloat16*>(out));
             B2_CUDA_OK(cudaGetLastError());
             return B2_OK;
@@ -585,7 +772,8 @@ extern "C" int b2_chunk_attention(void* out, const void* q, const void* k_cache,
     }
     B2_DISPATCH_ACT(act_dtype, A, (chunk_attention_kernel<A><<<blocks, warps * 32, smem, st>>>(
         static_cast<const A*>(q), static_cast<const A*>(k_cache), static_cast<const A*>(v_cache), block_tables, max_nb, cu_q,
-        ctx_start, n_seq, T, H, G, dk, dv, bs, scale, chunk, sink, sink_logit, skip_from, static_cast<A*>(out))));
+        ctx_start, n_seq, T, H, G, dk, dv, bs, scale, chunk, window, keep_first, sink, sink_logit, sink_logits,
+        static_cast<const A*>(gate), gate_stride, skip_from, static_cast<A*>(out))));
     B2_CUDA_OK(cudaGetLastError());
     return B2_OK;
 }

@@ -16,7 +16,8 @@
 //
 // The same three stages serve other linear recurrences over a matrix state (b2_recur_prep, b2_channel_scan,
 // b2_gated_head_norm): the decay may act per key channel instead of per head (decay [T, H, dk], computed in fp32 from a
-// separate fp32 input a [T, H*dk]: exp(-exp(A_log[h]) softplus(a + bias)) or sigmoid(a + bias)^(1/tau)), the write may be
+// separate fp32 input a [T, H*dk]: exp(-exp(A_log[h]) softplus(a + bias)) or sigmoid(a + bias)^(1/tau)) or be one fixed
+// number per head (linear attention with a constant decay: S <- lambda_h S + k v^T), the write may be
 // the plain outer product k v^T instead of the delta correction (gated linear attention: S <- diag(decay) S + k v^T),
 // the convolution, its activation and the unit-vector step are optional, and the output gate is SiLU or a sigmoid of
 // a gate row given on its own.  With a decay per channel the decay is applied first: S <- diag(g) S; u = beta (v - S^T k).
@@ -99,6 +100,8 @@ __global__ void recur_prep_kernel(const T* __restrict__ proj, int64_t proj_strid
     if (sp.decay_mode == B2_DECAY_HEAD_SOFTPLUS) {
         for (int hh = threadIdx.x; hh < H; hh += blockDim.x)
             decay[(size_t)row * H + hh] = expf(-expf(sp.A_log[hh]) * b2::softplus_f(b2::ld(pr + sp.off_a + hh) + sp.bias[hh]));
+    } else if (sp.decay_mode == B2_DECAY_HEAD_CONST) {
+        for (int hh = threadIdx.x; hh < H; hh += blockDim.x) decay[(size_t)row * H + hh] = sp.bias[hh];
     } else {
         const float* ar = sp.a + (size_t)row * sp.a_stride;
         float* dr = decay + (size_t)row * H * dk;
@@ -421,6 +424,36 @@ __global__ void gated_head_norm_kernel(const float* __restrict__ o, const T* __r
     }
 }
 
+// The same for wide rows (a norm over all the heads of a token at once is one "head" of H * dv entries): a CTA per
+// (row, head), four entries a thread per access when the sizes and addresses allow.
+template <typename T, int W>
+__global__ void __launch_bounds__(256)
+gated_row_norm_kernel(const float* __restrict__ o, const T* __restrict__ gate, int64_t gate_stride, int gate_kind, int H, int dv,
+                      const float* __restrict__ norm_w, float eps, float out_scale, T* __restrict__ out, int64_t out_stride) {
+    __shared__ float red[33];
+    const int row = blockIdx.x / H, hh = blockIdx.x % H;
+    const float* ov = o + (size_t)blockIdx.x * dv;
+    const int step = blockDim.x * W;
+    float ss = 0.f;
+    for (int i = threadIdx.x * W; i < dv; i += step) {
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        if (W == 4) b2::ld4(ov + i, v); else v[0] = ov[i];
+#pragma unroll
+        for (int c = 0; c < W; ++c) ss = fmaf(v[c], v[c], ss);
+    }
+    const float inv = rsqrtf(b2::block_sum(ss, red) / (float)dv + eps) * out_scale;
+    const T* g = gate + (size_t)row * gate_stride + (size_t)hh * dv;
+    T* dst = out + (size_t)row * out_stride + (size_t)hh * dv;
+    for (int i = threadIdx.x * W; i < dv; i += step) {
+        float v[4] = {0.f, 0.f, 0.f, 0.f}, z[4] = {0.f, 0.f, 0.f, 0.f}, w[4] = {0.f, 0.f, 0.f, 0.f};
+        if (W == 4) { b2::ld4(ov + i, v); b2::ld4(g + i, z); b2::ld4(norm_w + i, w); }
+        else { v[0] = ov[i]; z[0] = b2::ld(g + i); w[0] = norm_w[i]; }
+#pragma unroll
+        for (int c = 0; c < W; ++c) v[c] *= inv * w[c] * (gate_kind == B2_GATE_SIGMOID ? b2::sigmoid_f(z[c]) : b2::silu_f(z[c]));
+        if (W == 4) b2::st4(dst + i, v); else b2::st(dst + i, v[0]);
+    }
+}
+
 template <bool CH, bool DELTA>
 int launch_scan(const float* qkv, const float* beta, const float* decay, int total_rows, int H, int G, int dk, int dv,
                 const int32_t* cu_q, const int32_t* ctx_start, const int32_t* state_slot, int n_seq, float* state, float* o,
@@ -523,13 +556,15 @@ extern "C" int b2_recur_prep(const void* proj, int64_t proj_stride, int act_dtyp
     B2_REQUIRE(T >= 0 && H > 0 && G > 0 && H % G == 0 && dk > 0 && dv > 0 && taps >= 1 && taps <= kMaxTaps, B2_EINVAL,
                "recur_prep: bad sizes H=%d G=%d dk=%d dv=%d taps=%d", H, G, dk, dv, taps);
     B2_REQUIRE(decay_mode == B2_DECAY_HEAD_SOFTPLUS || decay_mode == B2_DECAY_CHANNEL_SOFTPLUS ||
-               decay_mode == B2_DECAY_CHANNEL_SIGMOID_POW, B2_EINVAL, "recur_prep: unknown decay mode %d", decay_mode);
+               decay_mode == B2_DECAY_CHANNEL_SIGMOID_POW || decay_mode == B2_DECAY_HEAD_CONST, B2_EINVAL,
+               "recur_prep: unknown decay mode %d", decay_mode);
     if (T == 0 || n_seq == 0) return B2_OK;
     B2_REQUIRE(proj && cu_q && ctx_start && state_slot && qkv && decay, B2_EINVAL, "recur_prep: null pointer");
     B2_REQUIRE(conv_w || taps == 1, B2_EINVAL, "recur_prep: a convolution of %d taps needs its weights", taps);
     B2_REQUIRE(conv_state || taps == 1, B2_EINVAL, "recur_prep: a convolution of %d taps needs its state", taps);
     B2_REQUIRE(off_beta < 0 || beta, B2_EINVAL, "recur_prep: beta columns without an output");
     if (decay_mode == B2_DECAY_HEAD_SOFTPLUS) B2_REQUIRE(A_log && decay_bias && off_a >= 0, B2_EINVAL, "recur_prep: decay inputs missing");
+    else if (decay_mode == B2_DECAY_HEAD_CONST) B2_REQUIRE(decay_bias, B2_EINVAL, "recur_prep: the decay constants are missing");
     else B2_REQUIRE(a && a_stride >= (int64_t)H * dk, B2_EINVAL, "recur_prep: the decay input per channel is missing");
     if (decay_mode == B2_DECAY_CHANNEL_SOFTPLUS) B2_REQUIRE(A_log, B2_EINVAL, "recur_prep: A_log missing");
     if (decay_mode == B2_DECAY_CHANNEL_SIGMOID_POW) B2_REQUIRE(tau > 0.f, B2_EINVAL, "recur_prep: tau must be positive");
@@ -579,6 +614,21 @@ extern "C" int b2_gated_head_norm(const float* o, const void* gate, int64_t gate
     if (T == 0) return B2_OK;
     B2_REQUIRE(o && gate && norm_w && out, B2_EINVAL, "gated_head_norm: null pointer");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dv > 512) {                                  // wide rows: a CTA per (row, head) instead of a warp
+        const size_t esz = act_dtype == B2_ACT_BF16 ? 2 : 4;
+        const bool vec = dv % 4 == 0 && gate_stride % 4 == 0 && out_stride % 4 == 0 && b2_aligned16(o) && b2_aligned16(norm_w) &&
+                         reinterpret_cast<uintptr_t>(gate) % (4 * esz) == 0 && reinterpret_cast<uintptr_t>(out) % (4 * esz) == 0;
+        B2_DISPATCH_ACT(act_dtype, A, {
+            if (vec)
+                gated_row_norm_kernel<A, 4><<<T * H, 256, 0, st>>>(o, static_cast<const A*>(gate), gate_stride, gate_kind, H, dv,
+                                                                  norm_w, eps, out_scale, static_cast<A*>(out), out_stride);
+            else
+                gated_row_norm_kernel<A, 1><<<T * H, 256, 0, st>>>(o, static_cast<const A*>(gate), gate_stride, gate_kind, H, dv,
+                                                                  norm_w, eps, out_scale, static_cast<A*>(out), out_stride);
+        });
+        B2_CUDA_OK(cudaGetLastError());
+        return B2_OK;
+    }
     const int items = T * H, blocks = (items + 7) / 8;
     B2_DISPATCH_ACT(act_dtype, A, (gated_head_norm_kernel<A><<<blocks, 256, 0, st>>>(o, static_cast<const A*>(gate), gate_stride,
                                                                                     gate_kind, H, dv, norm_w, eps, out_scale,

@@ -12,6 +12,8 @@
 //                         and written behind the absorbed part of qa; when the layer owns a down-projection its first R
 //                         outputs are RMS-normed (plain weight) into the cache row at the token's slot and the last dr,
 //                         rotated, behind them.  A layer that reads another layer's pool passes dkv_off < 0.
+//   b2_latent_prep_rows   the same with the query heads and the down-projection in rows of two different buffers (a design
+//                         whose queries come out of a second product, behind a query latent).
 //   b2_latent_attention   o[t, h, :R] = gate[t, h] * sum_j softmax_j(s)[j] c_j over the visible keys: j <= i, and with a
 //                         window W > 0 also i - j < W.  gate = sigmoid of a per-head column of the projection rows
 //                         (gate NULL: 1).  Softmax state, scores and the accumulator are fp32.
@@ -27,7 +29,8 @@ namespace {
 constexpr int kMaxRPerLane = 32;                     // R <= 1024 in the warp kernel
 
 template <typename T>
-__global__ void latent_prep_kernel(const T* __restrict__ proj, int64_t proj_stride, int H, int dn, int dr, int rot_dims, int R,
+__global__ void latent_prep_kernel(const T* __restrict__ proj, int64_t proj_stride, const T* __restrict__ kv, int64_t kv_stride,
+                                   int H, int dn, int dr, int rot_dims, int R,
                                    int q_off, int dkv_off, const float* __restrict__ norm_w, float eps,
                                    const int32_t* __restrict__ positions, const float* __restrict__ cos_sin, int max_pos,
                                    const int64_t* __restrict__ slots, int bs, T* __restrict__ qa, T* __restrict__ cache) {
@@ -55,7 +58,7 @@ __global__ void latent_prep_kernel(const T* __restrict__ proj, int64_t proj_stri
     const int64_t slot = slots[t];
     if (slot < 0) return;                            // uniform over the block
     T* dst = cache + (size_t)slot * Dc;
-    const T* src = row + dkv_off;
+    const T* src = kv + (size_t)t * kv_stride + dkv_off;      // the down-projection may live in rows of its own
     float ss = 0.f;
     for (int i = threadIdx.x; i < R; i += blockDim.x) {
         const float v = b2::ld(src + i);
@@ -77,7 +80,8 @@ __global__ void latent_prep_kernel(const T* __restrict__ proj, int64_t proj_stri
 
 // The same with four elements per access (8 or 16 bytes) for row layouts whose offsets are all multiples of four.
 template <typename T>
-__global__ void latent_prep_vec_kernel(const T* __restrict__ proj, int64_t proj_stride, int H, int dn, int dr, int rot_dims, int R,
+__global__ void latent_prep_vec_kernel(const T* __restrict__ proj, int64_t proj_stride, const T* __restrict__ kv,
+                                       int64_t kv_stride, int H, int dn, int dr, int rot_dims, int R,
                                        int q_off, int dkv_off, const float* __restrict__ norm_w, float eps,
                                        const int32_t* __restrict__ positions, const float* __restrict__ cos_sin, int max_pos,
                                        const int64_t* __restrict__ slots, T* __restrict__ qa, T* __restrict__ cache) {
@@ -110,7 +114,7 @@ __global__ void latent_prep_vec_kernel(const T* __restrict__ proj, int64_t proj_
     const int64_t slot = slots[t];
     if (slot < 0) return;                            // uniform over the block
     T* dst = cache + (size_t)slot * Dc;
-    const T* src = row + dkv_off;
+    const T* src = kv + (size_t)t * kv_stride + dkv_off;      // the down-projection may live in rows of its own
     float ss = 0.f;
     for (int i = threadIdx.x * 4; i < R; i += blockDim.x * 4) {
         float v[4];
@@ -945,26 +949,35 @@ extern "C" int b2_latent_prep(const void* proj, int64_t proj_stride, int act_dty
                               int R, int q_off, int dkv_off, const float* norm_w, float eps, const int32_t* positions,
                               const float* cos_sin, int max_pos, const int64_t* slots, int bs, void* qa, void* cache,
                               void* stream) {
+    return b2_latent_prep_rows(proj, proj_stride, proj, proj_stride, act_dtype, T, H, dn, dr, rot_dims, R, q_off, dkv_off, norm_w,
+                               eps, positions, cos_sin, max_pos, slots, bs, qa, cache, stream);
+}
+
+extern "C" int b2_latent_prep_rows(const void* q, int64_t q_stride, const void* kv, int64_t kv_stride, int act_dtype, int T, int H,
+                                   int dn, int dr, int rot_dims, int R, int q_off, int dkv_off, const float* norm_w, float eps,
+                                   const int32_t* positions, const float* cos_sin, int max_pos, const int64_t* slots, int bs,
+                                   void* qa, void* cache, void* stream) {
     B2_REQUIRE(T >= 0 && H > 0 && dn >= 0 && dr >= 0 && R > 0 && bs > 0 && q_off >= 0 && rot_dims >= 0 && rot_dims <= dr &&
                    rot_dims % 2 == 0 && max_pos > 0, B2_EINVAL, "latent_prep: bad sizes");
     if (T == 0) return B2_OK;
-    B2_REQUIRE(proj && positions && qa && (rot_dims == 0 || cos_sin), B2_EINVAL, "latent_prep: null pointer");
-    B2_REQUIRE(dkv_off < 0 || (slots && cache), B2_EINVAL, "latent_prep: a layer with a down-projection needs slots and its pool");
+    B2_REQUIRE(q && positions && qa && (rot_dims == 0 || cos_sin), B2_EINVAL, "latent_prep: null pointer");
+    B2_REQUIRE(dkv_off < 0 || (slots && cache && kv), B2_EINVAL,
+               "latent_prep: a layer with a down-projection needs its rows, slots and its pool");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int work = H * dr > R ? H * dr : R;
     const int threads = work >= 2048 ? 256 : 128;
-    const bool vec = proj_stride % 4 == 0 && q_off % 4 == 0 && dn % 4 == 0 && dr % 4 == 0 && R % 4 == 0 && rot_dims % 4 == 0 &&
-                     (dkv_off < 0 || dkv_off % 4 == 0) && b2_aligned16(proj) && b2_aligned16(qa) &&
-                     (dkv_off < 0 || b2_aligned16(cache));
+    const bool vec = q_stride % 4 == 0 && q_off % 4 == 0 && dn % 4 == 0 && dr % 4 == 0 && R % 4 == 0 && rot_dims % 4 == 0 &&
+                     (dkv_off < 0 || (dkv_off % 4 == 0 && kv_stride % 4 == 0 && b2_aligned16(kv))) && b2_aligned16(q) &&
+                     b2_aligned16(qa) && (dkv_off < 0 || b2_aligned16(cache));
     B2_DISPATCH_ACT(act_dtype, A, {
         if (vec)
-            latent_prep_vec_kernel<A><<<T, threads, 0, st>>>(static_cast<const A*>(proj), proj_stride, H, dn, dr, rot_dims, R, q_off,
-                                                             dkv_off, norm_w, eps, positions, cos_sin, max_pos, slots,
-                                                             static_cast<A*>(qa), static_cast<A*>(cache));
+            latent_prep_vec_kernel<A><<<T, threads, 0, st>>>(static_cast<const A*>(q), q_stride, static_cast<const A*>(kv), kv_stride,
+                                                             H, dn, dr, rot_dims, R, q_off, dkv_off, norm_w, eps, positions,
+                                                             cos_sin, max_pos, slots, static_cast<A*>(qa), static_cast<A*>(cache));
         else
-            latent_prep_kernel<A><<<T, threads, 0, st>>>(static_cast<const A*>(proj), proj_stride, H, dn, dr, rot_dims, R, q_off,
-                                                         dkv_off, norm_w, eps, positions, cos_sin, max_pos, slots, bs,
-                                                         static_cast<A*>(qa), static_cast<A*>(cache));
+            latent_prep_kernel<A><<<T, threads, 0, st>>>(static_cast<const A*>(q), q_stride, static_cast<const A*>(kv), kv_stride, H,
+                                                         dn, dr, rot_dims, R, q_off, dkv_off, norm_w, eps, positions, cos_sin,
+                                                         max_pos, slots, bs, static_cast<A*>(qa), static_cast<A*>(cache));
     });
     B2_CUDA_OK(cudaGetLastError());
     return B2_OK;

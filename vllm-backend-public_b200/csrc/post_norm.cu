@@ -8,6 +8,9 @@
 //                      norm = layer norm (B2_NORM_LAYER, bias optional) or RMS norm (B2_NORM_RMS), eps inside the root.
 //                      The write-back and the next read-out touch the same row, so the op moves D*4 in, D*4 out for the
 //                      residual plus one activation row each way.  With post_w = NULL it is residual add + pre-norm.
+//   b2_row_norm        out[t, :] = in[t, :] / sqrt(mean(in[t, :]^2) + eps) * w over activation rows of any width (row strides
+//                      of their own: a column range of a wider projection is fine); the statistics in fp32.  The norm of a
+//                      low-rank latent between its two projections.
 //   b2_relu_sq         out = max(in, 0)^2
 //   b2_glu_and_mul     out[t, i] = glu(in[t, i], in[t, I + i]) for rows [gate | up]: SiLU(g) * u (B2_GLU_SILU) or the bounded
 //                      unit g' * sigmoid(alpha g') * (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit) (B2_GLU_CLAMPED)
@@ -100,6 +103,62 @@ sandwich_norm_kernel(float* __restrict__ x, int D, const T* __restrict__ y, int6
 #pragma unroll
         for (int c = 0; c < W; ++c) v[c] = (row_sm[d + c] - mean) * inv * pre_w[d + c] + (pre_b ? pre_b[d + c] : 0.f);
         if (W == 4) b2::st4(ho + d, v); else b2::st(ho + d, v[0]);
+    }
+}
+
+// W = 4: 16-byte (fp32) or 8-byte (bf16) accesses, the row kept in registers between the two passes when it fits (up to
+// kRowNormKeep accesses a thread); W = 1: any width and alignment.
+constexpr int kRowNormKeep = 4;
+
+template <typename T, int W>
+__global__ void __launch_bounds__(256)
+row_norm_kernel(T* __restrict__ out, int64_t out_stride, const T* __restrict__ in, int64_t in_stride, int n,
+                const float* __restrict__ w, float eps) {
+    __shared__ float red[33];
+    const T* src = in + (size_t)blockIdx.x * in_stride;
+    T* dst = out + (size_t)blockIdx.x * out_stride;
+    const int step = blockDim.x * W;
+    const bool keep = n <= kRowNormKeep * step;
+    float held[kRowNormKeep][4];
+    float ss = 0.f;
+    if (keep) {
+#pragma unroll
+        for (int r = 0; r < kRowNormKeep; ++r) {
+            const int i = threadIdx.x * W + r * step;
+            held[r][0] = held[r][1] = held[r][2] = held[r][3] = 0.f;
+            if (i < n) {
+                if (W == 4) b2::ld4(src + i, held[r]); else held[r][0] = b2::ld(src + i);
+            }
+#pragma unroll
+            for (int c = 0; c < W; ++c) ss = fmaf(held[r][c], held[r][c], ss);
+        }
+    } else {
+        for (int i = threadIdx.x * W; i < n; i += step) {
+            float v[4] = {0.f, 0.f, 0.f, 0.f};
+            if (W == 4) b2::ld4(src + i, v); else v[0] = b2::ld(src + i);
+#pragma unroll
+            for (int c = 0; c < W; ++c) ss = fmaf(v[c], v[c], ss);
+        }
+    }
+    const float inv = rsqrtf(b2::block_sum(ss, red) / (float)n + eps);
+    if (keep) {
+#pragma unroll
+        for (int r = 0; r < kRowNormKeep; ++r) {
+            const int i = threadIdx.x * W + r * step;
+            if (i < n) {
+#pragma unroll
+                for (int c = 0; c < W; ++c) held[r][c] *= inv * (w ? w[i + c] : 1.f);
+                if (W == 4) b2::st4(dst + i, held[r]); else b2::st(dst + i, held[r][0]);
+            }
+        }
+    } else {
+        for (int i = threadIdx.x * W; i < n; i += step) {
+            float v[4] = {0.f, 0.f, 0.f, 0.f};
+            if (W == 4) b2::ld4(src + i, v); else v[0] = b2::ld(src + i);
+#pragma unroll
+            for (int c = 0; c < W; ++c) v[c] *= inv * (w ? w[i + c] : 1.f);
+            if (W == 4) b2::st4(dst + i, v); else b2::st(dst + i, v[0]);
+        }
     }
 }
 
@@ -205,6 +264,27 @@ extern "C" int b2_sandwich_norm(float* x, int T, int D, const void* y, int64_t y
         else B2_SANDWICH(1);
     });
 #undef B2_SANDWICH
+    B2_CUDA_OK(cudaGetLastError());
+    return B2_OK;
+}
+
+extern "C" int b2_row_norm(void* out, int64_t out_stride, const void* in, int64_t in_stride, int act_dtype, int T, int n,
+                           const float* w, float eps, void* stream) {
+    B2_REQUIRE(T >= 0 && n > 0 && out_stride >= n && in_stride >= n, B2_EINVAL, "row_norm: bad sizes");
+    if (T == 0) return B2_OK;
+    B2_REQUIRE(out && in, B2_EINVAL, "row_norm: null pointer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t esz = act_dtype == B2_ACT_BF16 ? 2 : 4;
+    const bool vec = n % 4 == 0 && in_stride % 4 == 0 && out_stride % 4 == 0 && reinterpret_cast<uintptr_t>(in) % (4 * esz) == 0 &&
+                     reinterpret_cast<uintptr_t>(out) % (4 * esz) == 0;
+    const int per = vec ? 4 : 1;
+    const int threads = n >= 1024 * per ? 256 : (n >= 256 * per ? 128 : 64);
+    B2_DISPATCH_ACT(act_dtype, A, {
+        if (vec)
+            row_norm_kernel<A, 4><<<T, threads, 0, st>>>(static_cast<A*>(out), out_stride, static_cast<const A*>(in), in_stride, n, w, eps);
+        else
+            row_norm_kernel<A, 1><<<T, threads, 0, st>>>(static_cast<A*>(out), out_stride, static_cast<const A*>(in), in_stride, n, w, eps);
+    });
     B2_CUDA_OK(cudaGetLastError());
     return B2_OK;
 }
