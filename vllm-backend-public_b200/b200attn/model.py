@@ -406,10 +406,11 @@ class LlamaModel:
 
 
 def _register_families() -> None:
-    from . import gatolix, kofadra, tonilix
+    from . import gatolix, kofadra, sanarax, tonilix
     ARCHITECTURES[kofadra.ARCHITECTURE] = kofadra.config_from_dir
     ARCHITECTURES[gatolix.ARCHITECTURE] = gatolix.config_from_dir
     ARCHITECTURES[tonilix.ARCHITECTURE] = tonilix.config_from_dir
+    ARCHITECTURES[sanarax.ARCHITECTURE] = sanarax.config_from_dir
 
 
 _register_families()
