@@ -710,7 +710,7 @@ def main():
     ap.add_argument("--batch", type=int, default=0, help="override the workload batch size (experiments only)")
     ap.add_argument("--ragged", action="store_true",
                     help="experiment: sequence lengths log-uniform in [128, ctx] instead of all = ctx")
-    ap.add_argument("--family", default=None, choices=["kofadra", "gatolix", "tonilix"],
+    ap.add_argument("--family", default=None, choices=["kofadra", "gatolix", "tonilix", "sanarax"],
                     help="instead of the headline workload: prefill / decode throughput and per-kernel rooflines of that "
                          "model family beside the Llama model of equal size (bench_families.py; JSON lines)")
     ap.add_argument("--family-sizes", default="2k,4k", help="comma-separated sizes of bench_families.SIZES")

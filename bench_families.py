@@ -1,7 +1,9 @@
-"""`bench.py --family kofadra|gatolix|tonilix`: prefill and decode throughput of a model family at layer sizes of real models
+"""`bench.py --family kofadra|gatolix|tonilix|sanarax`: prefill and decode throughput of a model family at layer sizes of real models
 (random weights), beside the Llama model of equal width, heads, head size and ACTIVE feed-forward width, plus the device
 time of every kernel of the family with the roofline that bounds it beside the like kernel of the Llama path (Tonilix:
-beside the Kofadra family, whose recurrent mixer, attention without rotation and routed experts are the closest).
+beside the Kofadra family, whose recurrent mixer, attention without rotation and routed experts are the closest; Sanarax:
+beside the Gatolix family, whose norms on both sides, latent attention and squared-ReLU feed-forward are the closest, with
+the like kernel of Kofadra and Tonilix for the sink attention and the linear attention).
 
 Both models run through the same engine (LLMEngine.replay_step: scheduler, pools, state slots, CUDA-graph decode).
   prefill   one prompt chunk of T tokens in one step; wall clock around the step (it ends with a stream synchronize)
@@ -30,6 +32,16 @@ GATOLIX_SIZES = {
                top=4, vocab=32000, window=1024),
     "4k": dict(hidden=4096, layers=4, heads=32, kv_heads=8, dim=128, rot_dim=64, vdim=128, kv_rank=512, ff=1792, experts=64,
                top=8, vocab=32000, window=1024),
+}
+
+
+# Sanarax: the head geometry of SIZES, the latent geometry of GATOLIX_SIZES, a dense feed-forward of the active width; six
+# layers = two of each mixer, the second three on the tensors of the first three
+SANARAX_SIZES = {
+    "2k": dict(hidden=2048, layers=6, heads=16, kv_heads=4, head_dim=128, ff=4096, vocab=32000, kv_rank=512, q_rank=1536,
+               rot_dim=64, window=1024, keep_first=4),
+    "4k": dict(hidden=4096, layers=6, heads=32, kv_heads=8, head_dim=128, ff=14336, vocab=32000, kv_rank=512, q_rank=1536,
+               rot_dim=64, window=1024, keep_first=4),
 }
 
 
@@ -466,10 +478,151 @@ def _kernels_tonilix(size, s, B, ctx, T):
         torch.cuda.empty_cache()
 
 
+def _kernels_sanarax(size, s, B, ctx, T):
+    """Device time of the Sanarax kernels and of the like kernels of Gatolix, Kofadra and Tonilix on the same shapes."""
+    import torch
+    from b200attn import ops
+    dev = torch.device("cuda", 0)
+    HBM, TF, src = _peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    D, H, G, d, F = s["hidden"], s["heads"], s["kv_heads"], s["head_dim"], s["ff"]
+    R, Rq, dr, W, keep = s["kv_rank"], s["q_rank"], s["rot_dim"], s["window"], s["keep_first"]
+    Dc = R + dr
+    bf = torch.bfloat16
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)          # noqa: E731
+
+    def line(kernel, phase, ms, bytes_=0, flops=0, like=None):
+        gbs, tfs = bytes_ / ms / 1e6, flops / ms / 1e9
+        _emit(bench="kernel", size=size, kernel=kernel, phase=phase, ms=round(ms, 4), gb_per_s=round(gbs, 1),
+              tflop_per_s=round(tfs, 2), frac_hbm=round(gbs / HBM, 3), frac_bf16=round(tfs / TF, 4), peaks=src, like=like)
+
+    tab_w = ops.rotary_table(ctx + T + 64, d // 2, 1e6, None, dev)
+    tab_l = ops.rotary_table(ctx + T + 64, dr, 1e4, None, dev)
+    for phase, n_seq, q_len, c in (("prefill", 1, T, 0), ("decode", B, 1, ctx)):
+        rows = n_seq * q_len
+        nb_seq = (c + q_len + 15) // 16
+        tables = torch.arange(n_seq * nb_seq, dtype=torch.int32, device=dev).view(n_seq, nb_seq)
+        batch = ops.SeqBatch(i32([i * q_len for i in range(n_seq + 1)]), i32([c] * n_seq), tables, i32(list(range(n_seq))),
+                             n_seq, rows)
+        pos = (torch.arange(rows, device=dev) % q_len + c).to(torch.int32)
+        slots = (torch.arange(rows, device=dev) // q_len * (nb_seq * 16) + pos).to(torch.int64)
+        # ---- RMS norm after the sublayer + residual + RMS norm before the next  |  like: Gatolix's two layer norms
+        x = torch.randn(rows, D, device=dev)
+        y = torch.randn(rows, D, device=dev).to(bf)
+        ws = [torch.ones(D, device=dev) for _ in range(4)]
+        ms = _time(lambda: ops.sandwich_norm(x, y, ws[0], None, ws[1], None, eps=1e-6, norm_kind=ops.NORM_RMS, h_dtype=bf), flush)
+        line("sandwich_norm (2 RMS norms, fp32 residual)", phase, ms, bytes_=rows * D * (4 + 4 + 2 + 2), like="sandwich_norm (Gatolix)")
+        ms = _time(lambda: ops.sandwich_norm(x, y, *ws, eps=1e-6, h_dtype=bf), flush)
+        line("sandwich_norm (Gatolix, 2 layer norms)", phase, ms, bytes_=rows * D * (4 + 4 + 2 + 2))
+        # ---- window attention: rotation + pool write  |  like: Tonilix's query temperature + pool write
+        kc = torch.randn(n_seq * nb_seq, G, 16, d, device=dev).to(bf)
+        vc = torch.randn(n_seq * nb_seq, G, 16, d, device=dev).to(bf)
+        qk = torch.randn(rows, (H + G) * d + H, device=dev).to(bf)
+        ms = _time(lambda: ops.qk_rope_cache(qk, H, G, d, d, pos, tab_w, d // 2, slots, kc, vc, v_from_k=True), flush)
+        line("qk_rope_cache (half of every head turns; values = unrotated keys)", phase, ms, bytes_=rows * (2 * H + 3 * G) * d * 2,
+             like="qk_prep_cache (Tonilix)")
+        qkv = torch.randn(rows, (H + 2 * G) * d, device=dev).to(bf)
+        ms = _time(lambda: ops.qk_prep_cache(qkv, H, G, d, d, slots, kc, vc, pos, 0.25, 512), flush)
+        line("qk_prep_cache (Tonilix)", phase, ms, bytes_=rows * (2 * H + 4 * G) * d * 2)
+        # ---- the attention itself  |  like: Kofadra's mask blocks of the same size with one sink
+        q = torch.randn(rows, H, d, device=dev).to(bf)
+        sinks = torch.randn(H, device=dev)
+        gate = qk[:, (H + G) * d:]
+        ms = _time(lambda: ops.chunk_attention(q, kc, vc, batch, d ** -0.5, window=W, keep_first=keep, sink=1.0, sink_logits=sinks,
+                                               gate=gate), flush)
+        name = "chunk_attention (window %d + %d kept, sink per head, gate)" % (W, keep)
+        if phase == "prefill":
+            pairs = sum(min(p + 1, W) + max(0, min(keep, p - W + 1)) for p in range(T))
+            line(name, phase, ms, flops=4 * pairs * H * d, like="chunk_attention (Kofadra)")
+            ms = _time(lambda: ops.chunk_attention(q, kc, vc, batch, d ** -0.5, W, sink=1.0), flush)
+            line("chunk_attention (Kofadra: blocks of %d, sink)" % W, phase, ms, flops=4 * sum(p % W + 1 for p in range(T)) * H * d)
+        else:
+            seen = min(c + 1, W) + max(0, min(keep, c - W + 1))
+            line(name, phase, ms, bytes_=n_seq * seen * G * 2 * d * 2, like="chunk_attention (Kofadra)")
+            ms = _time(lambda: ops.chunk_attention(q, kc, vc, batch, d ** -0.5, W, sink=1.0), flush)
+            line("chunk_attention (Kofadra: blocks of %d, sink)" % W, phase, ms, bytes_=n_seq * (c % W + 1) * G * 2 * d * 2)
+        # ---- latent attention: norm of the query latent, rotation + pool write from two buffers  |  like: Gatolix's
+        P = Rq + 8 * ((H + 7) // 8) + Dc
+        proj = torch.randn(rows, P, device=dev).to(bf)
+        nq, nw = torch.ones(Rq, device=dev), torch.ones(R, device=dev)
+        ms = _time(lambda: ops.row_norm(proj[:, :Rq], nq, 1e-6), flush)
+        line("row_norm (query latent of %d)" % Rq, phase, ms, bytes_=rows * Rq * 4, like="rms_norm (Llama)")
+        xq, wq = torch.randn(rows, Rq, device=dev).to(bf), torch.ones(Rq, device=dev).to(bf)
+        ms = _time(lambda: ops.rms_norm(xq, wq, 1e-6), flush)
+        line("rms_norm (Llama, same rows)", phase, ms, bytes_=rows * Rq * 4)
+        qh = torch.randn(rows, H * (d + dr), device=dev).to(bf)
+        cache = torch.randn(n_seq * nb_seq, 16, Dc, device=dev).to(bf)
+        ms = _time(lambda: ops.latent_prep(qh, H, d, dr, dr, R, 0, P - Dc, nw, 1e-6, pos, tab_l, slots, cache, kv=proj), flush)
+        line("latent_prep (queries and down-projection in two buffers)", phase, ms, bytes_=rows * (H * dr * 4 + Dc * 4),
+             like="latent_prep (Gatolix)")
+        Pg = H * (d + dr) + 8 * ((H + 7) // 8) + Dc
+        pg = torch.randn(rows, Pg, device=dev).to(bf)
+        ms = _time(lambda: ops.latent_prep(pg, H, d, dr, dr, R, 0, Pg - Dc, nw, 1e-6, pos, tab_l, slots, cache), flush)
+        line("latent_prep (Gatolix, one buffer)", phase, ms, bytes_=rows * (H * dr * 4 + Dc * 4))
+        qa = torch.randn(rows, H, Dc, device=dev).to(bf)
+        lgate = proj[:, Rq:Rq + H]
+        if phase == "prefill":
+            # a long portion: pool rows gathered, keys and values rebuilt per head, causal attention over them
+            cu, cs = i32([0, T]), i32([0])
+            lat = ops.latent_gather(cache, tables, cu, cs, 1, T)
+            kn = torch.randn(T, H, d, device=dev).to(bf)
+            vb = torch.randn(T, H, d, device=dev).to(bf)
+            q3 = qh.view(rows, H, d + dr)
+            ms = _time(lambda: ops.window_attention(q3[:, :, :d], qa[:, :, R:], kn, lat[:, R:], vb, cu, cs, cu, cs, 1, 0.07, 0,
+                                                    gate=lgate), flush)
+            line("window_attention (per-head keys, causal)", phase, ms, flops=2 * (T * (T + 1) // 2) * H * (2 * d + dr),
+                 like="window_attention (Gatolix)")
+            ms = _time(lambda: ops.window_attention(q3[:, :, :d], qa[:, :, R:], kn, lat[:, R:], vb, cu, cs, cu, cs, 1, 0.07, W,
+                                                    gate=lgate), flush)
+            line("window_attention (Gatolix, window %d)" % W, phase, ms, flops=2 * sum(min(p + 1, W) for p in range(T)) * H * (2 * d + dr))
+        else:
+            ms = _time(lambda: ops.latent_attention(qa, cache, batch, R, 0.07, 0, gate=lgate), flush)
+            line("latent_attention (causal)", phase, ms, bytes_=n_seq * (c + 1) * Dc * 2 + rows * H * (Dc + R) * 2,
+                 flops=2 * n_seq * (c + 1) * H * (Dc + R), like="latent_attention (Gatolix)")
+            ms = _time(lambda: ops.latent_attention(qa, cache, batch, R, 0.07, W, gate=lgate), flush)
+            seen = min(W, c + 1)
+            line("latent_attention (Gatolix, window %d)" % W, phase, ms, bytes_=n_seq * seen * Dc * 2 + rows * H * (Dc + R) * 2,
+                 flops=2 * n_seq * seen * H * (Dc + R))
+        # ---- linear attention with a fixed decay per head  |  like: Tonilix's gated linear attention (decay per key channel)
+        C = 3 * H * d
+        lp = torch.randn(rows, C + H * d, device=dev).to(bf)
+        dec = torch.full((H,), 0.99, device=dev)
+        prep = lambda: ops.recur_prep(lp, H, H, d, d, batch, conv_silu=True, decay_mode=ops.DECAY_HEAD_CONST, decay_bias=dec)  # noqa: E731
+        ms = _time(prep, flush)
+        line("recur_prep (SiLU, fixed decay)", phase, ms, bytes_=rows * (C * 2 + C * 4 + 4 * H), like="recur_prep (Tonilix)")
+        a = torch.randn(rows, H * d, device=dev)
+        ab = torch.zeros(H * d, device=dev)
+        prep_t = lambda: ops.recur_prep(lp, H, H, d, d, batch, q_scale=d ** -0.5, decay_mode=ops.DECAY_CHANNEL_SIGMOID_POW, a=a,  # noqa: E731
+                                        decay_bias=ab, tau=8.0)
+        ms = _time(prep_t, flush)
+        line("recur_prep (Tonilix: decay per key channel)", phase, ms, bytes_=rows * (C * 2 + C * 4 + H * d * 8))
+        state = torch.zeros(n_seq, H, d, d, device=dev)
+        qkv32, _, decay = prep()
+        ms = _time(lambda: ops.channel_scan(qkv32, None, decay, H, H, d, d, batch, state, delta=False), flush)
+        line("channel_scan (fixed decay per head)", phase, ms, flops=6 * rows * H * d * d,
+             bytes_=n_seq * H * d * d * 4 * 2 + rows * (C + H * d) * 4, like="channel_scan (Tonilix)")
+        _, _, decay_c = prep_t()
+        ms = _time(lambda: ops.channel_scan(qkv32, None, decay_c, H, H, d, d, batch, state, delta=False), flush)
+        line("channel_scan (Tonilix: decay per key channel)", phase, ms, flops=6 * rows * H * d * d,
+             bytes_=n_seq * H * d * d * 4 * 2 + rows * (C + 2 * H * d) * 4)
+        o32 = torch.randn(rows, H, d, device=dev)
+        nrow = torch.ones(H * d, device=dev)
+        ms = _time(lambda: ops.gated_head_norm(o32.view(rows, 1, H * d), lp[:, C:], nrow, 1e-6, ops.GATE_SIGMOID), flush)
+        line("gated_head_norm (one norm over all heads)", phase, ms, bytes_=rows * H * d * (4 + 2 + 2), like="gated_head_norm (Tonilix)")
+        ms = _time(lambda: ops.gated_head_norm(o32, lp[:, C:], nrow[:d].contiguous(), 1e-6, ops.GATE_SIGMOID), flush)
+        line("gated_head_norm (Tonilix: a norm per head)", phase, ms, bytes_=rows * H * d * (4 + 2 + 2))
+        # ---- feed-forward activation: the kernel Gatolix uses
+        act = torch.randn(rows, F, device=dev).to(bf)
+        ms = _time(lambda: ops.relu_sq(act), flush)
+        line("relu_sq (shared with Gatolix)", phase, ms, bytes_=rows * F * 4, like="relu_sq")
+        del kc, vc, cache, state, qkv32, lp, proj
+        torch.cuda.empty_cache()
+
+
 def run(family: str, sizes, steps: int, kernels: bool = True) -> None:
     import torch
     from b200attn.model import ModelConfig
-    if family not in ("kofadra", "gatolix", "tonilix"):
+    if family not in ("kofadra", "gatolix", "tonilix", "sanarax"):
         raise SystemExit(f"unknown family {family!r}")
     B, ctx, T = 64, 2560, 4096          # ctx: 2.5 mask blocks / windows of the bench geometries
     for name in sizes:
@@ -483,13 +636,19 @@ def run(family: str, sizes, steps: int, kernels: bool = True) -> None:
             s = SIZES[name]
             fcfg = bench_config(s["hidden"], s["layers"], s["heads"], s["kv_heads"], s["head_dim"], s["ff"], s["experts"],
                                 s["top"], s["vocab"], name=f"tonilix-{name}")
+        elif family == "sanarax":
+            from b200attn.sanarax import bench_config
+            s = SANARAX_SIZES[name]
+            fcfg = bench_config(s["hidden"], s["layers"], s["heads"], s["kv_heads"], s["head_dim"], s["ff"], s["vocab"],
+                                kv_rank=s["kv_rank"], q_rank=s["q_rank"], rot_dim=s["rot_dim"], window=s["window"],
+                                keep_first=s["keep_first"], name=f"sanarax-{name}")
         else:
             from b200attn.gatolix import bench_config
             s = GATOLIX_SIZES[name]
             fcfg = bench_config(s["hidden"], s["layers"], s["heads"], s["dim"], s["rot_dim"], s["vdim"], s["kv_rank"], s["ff"],
                                 s["experts"], s["top"], s["vocab"], window=s["window"], name=f"gatolix-{name}")
-        lcfg = ModelConfig(f"llama-{name}", s["hidden"], s["layers"], s["heads"], s["kv_heads"], s["top"] * s["ff"], s["vocab"],
-                           max_position=8192)
+        lcfg = ModelConfig(f"llama-{name}", s["hidden"], s["layers"], s["heads"], s["kv_heads"], s.get("top", 1) * s["ff"],
+                           s["vocab"], max_position=8192)
         _emit(bench="config", size=name, **s, **{f"{family}_params": fcfg.params}, llama_params=lcfg.params, prefill_tokens=T,
               decode_batch=B, decode_ctx=ctx, data="synthetic", dtype="bf16")
         _throughput(fcfg.name, fcfg, B, ctx, T, steps)
@@ -498,7 +657,14 @@ def run(family: str, sizes, steps: int, kernels: bool = True) -> None:
             kcfg = kofadra_config(s["hidden"], s["layers"], s["heads"], s["kv_heads"], s["head_dim"], s["ff"], s["experts"],
                                   s["top"], s["vocab"], streams=0, name=f"kofadra-{name}")
             _throughput(kcfg.name, kcfg, B, ctx, T, steps)
+        if family == "sanarax":                 # the closest family at equal size: norms on both sides, latent attention
+            from b200attn.gatolix import bench_config as gatolix_config
+            g = GATOLIX_SIZES[name]
+            gcfg = gatolix_config(s["hidden"], s["layers"], s["heads"], s["head_dim"], s["rot_dim"], s["head_dim"], s["kv_rank"],
+                                  g["ff"], g["experts"], g["top"], s["vocab"], window=s["window"], name=f"gatolix-{name}")
+            _throughput(gcfg.name, gcfg, B, ctx, T, steps)
         _throughput(lcfg.name, lcfg, B, ctx, T, steps)
         if kernels:
-            {"kofadra": _kernels_kofadra, "gatolix": _kernels_gatolix, "tonilix": _kernels_tonilix}[family](name, s, B, ctx, T)
+            {"kofadra": _kernels_kofadra, "gatolix": _kernels_gatolix, "tonilix": _kernels_tonilix,
+             "sanarax": _kernels_sanarax}[family](name, s, B, ctx, T)
         torch.cuda.empty_cache()
