@@ -1379,7 +1379,7 @@ def latent_attention(qa: torch.Tensor, cache: torch.Tensor, batch: SeqBatch, R: 
 
 def window_attention_ok(dtype: torch.dtype, dn: int, dr: int, dv: int) -> bool:
     """Shapes b2_window_attention takes."""
-    return dtype == torch.bfloat16 and dn % 8 == 0 and dr % 8 == 0 and (dn + dr) % 16 == 0 and dn + dr > 0 and dv % 16 == 0 \
+    return dtype == torch.bfloat16 and dn % 8 == 0 and dr % 8 == 0 and (dn + dr) % 16 == 0 and 0 < dn + dr <= 512 and dv % 16 == 0 \
         and 0 < dv <= 128
 
 
