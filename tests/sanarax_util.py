@@ -3,9 +3,13 @@ their windows and constants and in which optional parts they have.  Checkpoints,
 of kofadra_util."""
 import copy
 
-from kofadra_util import TOL, make_engine, rel_err, replay, save_checkpoint, tokens  # noqa: F401
+from kofadra_util import make_engine, rel_err, replay, save_checkpoint, tokens  # noqa: F401
 
 import sanarax_ref as R
+
+# rel_err bounds: the worst position in fp32 (the engine stands at 1e-6 .. 3e-6 on these geometries), the 80th percentile in
+# bf16 (4e-3 .. 8e-3)
+TOL = {"float32": 2e-5, "bfloat16": 3e-2}
 
 
 def dense(ff):
@@ -64,7 +68,7 @@ def cfg_c():      # windows of one token, of a page, of a page + 1, a kept prefi
                            window(2, 1, 16, 0.3, size=8, keep=20, rot_dims=16)], embed_scale=0.7, logit_scale=3.0)
 
 
-def cfg_d():      # no size a multiple of four besides none; the first layer uses a later layer's tensors
+def cfg_d():      # no size a multiple of four; the first layer uses a later layer's tensors
     ls = [None, latent(3, 6, 6, 10, 14, 10, 0.4, rot_dims=2, base=30.0, mlp=dense(22)),
           window(3, 1, 6, 0.5, size=5, keep=3, rot_dims=2, base=9.0, mlp=dense(14)),
           lightning(2, 6, 10, (0.6, 0.95))]
